@@ -1,0 +1,44 @@
+import ast
+import glob
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def golden_names():
+    return sorted(os.path.splitext(os.path.basename(p))[0]
+                  for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+
+
+def load_golden(name):
+    """Returns (inputs dict from the seeded generator, reference outputs dict)."""
+    import hashlib
+    from oracle import make_inputs
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    kw = ast.literal_eval(str(z["__kwargs__"]))
+    d = make_inputs(**kw)
+    h = hashlib.sha256()
+    for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "dy", "h0", "dhT"):
+        if d.get(k) is not None:
+            h.update(np.ascontiguousarray(d[k]).tobytes())
+    assert h.hexdigest() == str(z["__sha256__"]), "seeded inputs drifted from the fixture's"
+    ref = {k: z[k] for k in z.files if not k.startswith("__")}
+    return d, ref
+
+
+@pytest.fixture(scope="session")
+def have_cuda():
+    import torch
+    return torch.cuda.is_available()
