@@ -1,0 +1,134 @@
+/* naju_b200 — C ABI of the B200 (sm_100a) gated diagonal state-space scan.
+ *
+ * This is the drop-in boundary for the scan path of the Naju reference project:
+ * every entry point below replaces one of the calls its scan backends make into
+ * native code.  Reference citations are paths inside that project.
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers unless the name ends in _host.
+ *  - The library never allocates or frees device memory: the caller sizes
+ *    workspaces with the *_bytes() queries and owns every buffer.
+ *  - Every call is asynchronous on `stream` (a cudaStream_t passed as void*).
+ *  - Return value: 0 = ok, negative = rejected argument (NAJU_E_*), positive =
+ *    CUDA runtime error code of the failed launch.  Device-side conditions (a
+ *    bounded wait that ran out) are recorded in the workspace status word and
+ *    read back with naju_b200_read_status().
+ *  - Shapes follow naju/scan.py:3-12: u, f_logit, i_logit, y [B,T,D];
+ *    Bm, Cm [B,T,N]; D_skip [D]; states [B,D,N] fp32.  The sigmoid of both gate
+ *    logits is applied inside (naju/scan.py:81-82).
+ */
+#ifndef NAJU_B200_H_
+#define NAJU_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NAJU_B200_ABI_VERSION 1
+
+/* element types of caller tensors */
+enum { NAJU_F32 = 0, NAJU_BF16 = 1, NAJU_F16 = 2 };
+
+/* argument errors */
+enum {
+  NAJU_OK = 0,
+  NAJU_E_NULL = -1,      /* a required pointer is NULL */
+  NAJU_E_SHAPE = -2,     /* B,T,D,N out of range (N must be 1..128, as naju/cuda/naju_cuda.cu:222) */
+  NAJU_E_DTYPE = -3,     /* unsupported dtype combination */
+  NAJU_E_STRIDE = -4,    /* inner stride not 1 / row stride smaller than the row */
+  NAJU_E_WORKSPACE = -5, /* workspace too small or misaligned */
+  NAJU_E_ALIGN = -6      /* a pointer is not aligned to its element size */
+};
+
+/* device-side status bits, OR-ed into the workspace status word */
+enum {
+  NAJU_ST_LOOKBACK_TIMEOUT = 1, /* a bounded wait on a neighbouring chunk's carry ran out */
+  NAJU_ST_BAD_TILE = 2          /* internal tile index out of range (never expected) */
+};
+
+/* Problem description shared by forward and backward.
+ * Strides are in ELEMENTS.  The innermost (channel / state) stride of every
+ * tensor is 1.  u/f_logit/i_logit may each have their own batch and time
+ * strides (the mixer hands Bm and Cm as two views of one [B,T,2N] tensor,
+ * naju/mixer.py:116, so their time stride is 2N there). */
+typedef struct naju_scan_desc {
+  int32_t B, T, D, N;
+  int32_t act_dtype;  /* u, y, dy, du            */
+  int32_t gate_dtype; /* f_logit, i_logit, and their gradients */
+  int32_t bc_dtype;   /* Bm, Cm, dB, dC          */
+  int32_t flags;      /* reserved, must be 0     */
+  int64_t u_sb, u_st;
+  int64_t fl_sb, fl_st;
+  int64_t il_sb, il_st;
+  int64_t bm_sb, bm_st;
+  int64_t cm_sb, cm_st;
+} naju_scan_desc;
+
+/* ABI version of the loaded library (NAJU_B200_ABI_VERSION it was built with). */
+int naju_b200_version(void);
+
+/* Human-readable text for a return code of this library. */
+const char* naju_b200_strerror(int code);
+
+/* Time steps per chunk of the forward/backward kernels for this problem (the spacing of
+ * the saved chunk-boundary states). */
+int naju_b200_chunk_len(const naju_scan_desc* desc);
+
+/* Bytes of the chunk-boundary state buffer the forward writes and the backward reads
+ * (the counterpart of the `ckpt` tensor of naju/cuda/naju_cuda.cu:45-46,246). */
+size_t naju_b200_ckpt_bytes(const naju_scan_desc* desc);
+
+/* Bytes of transient scratch for one forward / one backward call. */
+size_t naju_b200_fwd_scratch_bytes(const naju_scan_desc* desc);
+size_t naju_b200_bwd_scratch_bytes(const naju_scan_desc* desc);
+
+/* Forward scan.  Replaces ext.fwd / ext.fwd_chunked (naju/cuda/naju_cuda.cu:217-259,
+ * naju/cuda/__init__.py:48-54) and the Triton forwards (naju/chunk_triton.py:147-181,
+ * naju/chunk_affine_triton.py:256-290).
+ *   h0     optional [B,D,N] fp32 initial state (NULL = zeros, the reference behaviour)
+ *   y      [B,T,D] contiguous, act_dtype
+ *   hT     optional [B,D,N] fp32 final state
+ *   pT     optional [B,D] fp32 product of the retention gate over all T steps
+ *   ckpt   naju_b200_ckpt_bytes() bytes, 256-byte aligned; keep it for the backward
+ *   scratch naju_b200_fwd_scratch_bytes() bytes, 256-byte aligned; dead when the call has run
+ */
+int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit,
+                  const void* i_logit, const void* Bm, const void* Cm, const float* D_skip,
+                  const float* h0, void* y, float* hT, float* pT, void* ckpt, void* scratch,
+                  void* stream);
+
+/* Backward scan: all gradients in one pass over the sequence in reverse time.
+ * Replaces ext.bwd (naju/cuda/naju_cuda.cu:261-286) and naju_chunk_backward
+ * (naju/chunk_bwd_triton.py:187-243).
+ *   ckpt   the buffer the forward of the SAME inputs filled
+ *   dy     [B,T,D] contiguous act_dtype;  dhT optional [B,D,N] fp32 adjoint of hT
+ *   du [B,T,D] act_dtype; dfl, dil [B,T,D] gate_dtype; dB, dC [B,T,N] bc_dtype; all contiguous
+ *   dD [D] fp32;  dh0 optional [B,D,N] fp32
+ */
+int naju_b200_bwd(const naju_scan_desc* desc, const void* u, const void* f_logit,
+                  const void* i_logit, const void* Bm, const void* Cm, const float* D_skip,
+                  const float* h0, const void* dy, const float* dhT, const void* ckpt,
+                  void* du, void* dfl, void* dil, void* dB, void* dC, float* dD, float* dh0,
+                  void* scratch, void* stream);
+
+/* Single-token recurrent update for decode (one iteration of naju/scan.py:87-91; the
+ * reference has no such entry point).  state [B,D,N] fp32 is updated in place.
+ *   u, f_logit, i_logit, y : [B,D] with batch strides u_sb/fl_sb/il_sb (time strides unused)
+ *   Bm, Cm : [B,N] with batch strides bm_sb/cm_sb;  desc->T is ignored.
+ */
+int naju_b200_step(const naju_scan_desc* desc, float* state, const void* u, const void* f_logit,
+                   const void* i_logit, const void* Bm, const void* Cm, const float* D_skip,
+                   void* y, void* stream);
+
+/* Synchronises `stream` and returns the status word of a scratch buffer a forward or
+ * backward call used (0 = clean; NAJU_ST_* bits otherwise), or a negative/positive error
+ * code as above. */
+int naju_b200_read_status(const void* scratch, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NAJU_B200_H_ */

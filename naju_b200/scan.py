@@ -1,0 +1,238 @@
+"""Host side of the B200 gated scan: the reference's scan interface over the C ABI.
+
+Mirrors naju/scan.py of the reference project: the same `naju_scan` signature
+(naju/scan.py:75-76), the same tensor meaning (naju/scan.py:3-12) and the same backend
+selection rule (argument > NAJU_SCAN_BACKEND > default, naju/scan.py:48-52).  There is one
+implementation behind it — hand-written sm_100a CUDA in libnaju_b200.so — and no fallback:
+a CPU tensor or a missing library raises.
+
+Additive, keyword-only extensions the reference does not have: an initial state `h0`, the
+returned final state, and `naju_scan_step` for single-token decode.
+"""
+import os
+
+import torch
+
+from . import _lib
+
+# The reference's backend names are accepted so that existing configs keep working
+# (naju/mixer.py:121-122 forwards `scan_backend`); they all select the one CUDA path.
+_ALIASES = ("b200", "reference", "chunk", "cuda", "cuda_bw", "affine", "fused_affine_chunk")
+
+_DT = {torch.float32: _lib.NAJU_F32, torch.bfloat16: _lib.NAJU_BF16, torch.float16: _lib.NAJU_F16}
+
+
+def resolve_backend(backend=None):
+    """Same precedence as naju/scan.py:48-52; every valid name resolves to "b200"."""
+    b = backend or os.environ.get("NAJU_SCAN_BACKEND") or "b200"
+    b = b.lower()
+    if b not in _ALIASES:
+        raise ValueError(f"unknown scan backend {b!r}; valid: {', '.join(_ALIASES)}")
+    return "b200"
+
+
+def _check_status_enabled():
+    return os.environ.get("NAJU_B200_CHECK_STATUS", "0") == "1"
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _inner_contig(t):
+    """Tensors whose last stride is 1 and whose outer strides are non-negative pass through."""
+    if t.stride(-1) == 1 and all(s >= 0 for s in t.stride()) and t.data_ptr() % t.element_size() == 0:
+        if t.dim() < 3 or t.stride(-2) >= t.shape[-1]:
+            return t
+    return t.contiguous()
+
+
+def _prepare(u, f_logit, i_logit, Bm, Cm, D_skip):
+    if not u.is_cuda:
+        raise RuntimeError("naju_b200 scan needs CUDA tensors (there is no CPU fallback)")
+    if u.dim() != 3 or f_logit.shape != u.shape or i_logit.shape != u.shape:
+        raise ValueError("u, f_logit, i_logit must all be [B, T, D]")
+    if Bm.dim() != 3 or Bm.shape != Cm.shape or Bm.shape[:2] != u.shape[:2]:
+        raise ValueError("B and C must both be [B, T, N] matching u's batch and time")
+    if D_skip.shape != (u.shape[-1],):
+        raise ValueError("D_skip must be [D]")
+    if Bm.shape[-1] < 1 or Bm.shape[-1] > 128:
+        raise RuntimeError("d_state must be in 1..128")
+    if u.dtype not in _DT:
+        raise RuntimeError(f"unsupported dtype {u.dtype}")
+    # gates run in u's dtype or fp32 (autocast hands fp32 logits next to bf16 activations)
+    gdt = u.dtype if (f_logit.dtype == u.dtype and i_logit.dtype == u.dtype) else torch.float32
+    f_logit = f_logit.to(gdt)
+    i_logit = i_logit.to(gdt)
+    bdt = Bm.dtype if (Bm.dtype == Cm.dtype and Bm.dtype in _DT) else torch.float32
+    Bm, Cm = Bm.to(bdt), Cm.to(bdt)
+    u, f_logit, i_logit, Bm, Cm = map(_inner_contig, (u, f_logit, i_logit, Bm, Cm))
+    D_skip = D_skip.detach().to(torch.float32).contiguous()
+    return u, f_logit, i_logit, Bm, Cm, D_skip
+
+
+def _desc(u, f_logit, i_logit, Bm, Cm):
+    B, T, D = u.shape
+    d = _lib.ScanDesc()
+    d.B, d.T, d.D, d.N = B, T, D, Bm.shape[-1]
+    d.act_dtype, d.gate_dtype, d.bc_dtype = _DT[u.dtype], _DT[f_logit.dtype], _DT[Bm.dtype]
+    d.flags = 0
+    d.u_sb, d.u_st = u.stride(0), u.stride(1)
+    d.fl_sb, d.fl_st = f_logit.stride(0), f_logit.stride(1)
+    d.il_sb, d.il_st = i_logit.stride(0), i_logit.stride(1)
+    d.bm_sb, d.bm_st = Bm.stride(0), Bm.stride(1)
+    d.cm_sb, d.cm_st = Cm.stride(0), Cm.stride(1)
+    if T <= 1:  # a size-1 dimension may carry any stride; give the kernel a legal one
+        d.u_st, d.fl_st, d.il_st = max(d.u_st, D), max(d.fl_st, D), max(d.il_st, D)
+        d.bm_st, d.cm_st = max(d.bm_st, d.N), max(d.cm_st, d.N)
+    return d
+
+
+def _workspace(nbytes, device):
+    # torch's caching allocator returns 512-byte aligned blocks
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _state_arg(h, B, D, N, name):
+    if h is None:
+        return None
+    if h.shape != (B, D, N):
+        raise ValueError(f"{name} must be [B, D, N]")
+    return h.detach().to(torch.float32).contiguous()
+
+
+def scan_forward(u, f_logit, i_logit, Bm, Cm, D_skip, h0=None, want_final=False, want_decay=False):
+    """Raw forward over prepared tensors.  Returns (y, hT|None, pT|None, ckpt, desc)."""
+    lib = _lib.load()
+    B, T, D = u.shape
+    N = Bm.shape[-1]
+    d = _desc(u, f_logit, i_logit, Bm, Cm)
+    dev = u.device
+    y = torch.empty((B, T, D), dtype=u.dtype, device=dev)
+    hT = torch.empty((B, D, N), dtype=torch.float32, device=dev) if want_final else None
+    pT = torch.empty((B, D), dtype=torch.float32, device=dev) if want_decay else None
+    ckpt = _workspace(lib.naju_b200_ckpt_bytes(d), dev)
+    scratch = _workspace(lib.naju_b200_fwd_scratch_bytes(d), dev)
+    with torch.cuda.device(dev):
+        rc = lib.naju_b200_fwd(d, _ptr(u), _ptr(f_logit), _ptr(i_logit), _ptr(Bm), _ptr(Cm),
+                               _ptr(D_skip), _ptr(h0), _ptr(y), _ptr(hT), _ptr(pT), _ptr(ckpt),
+                               _ptr(scratch), _stream())
+        _lib.check(rc, "naju_b200_fwd")
+        if _check_status_enabled() and B * T * D > 0:
+            st = lib.naju_b200_read_status(_ptr(scratch), _stream())
+            if st != 0:
+                raise RuntimeError(f"naju_b200_fwd device status {st} (bounded wait ran out)")
+    return y, hT, pT, ckpt, d
+
+
+def scan_backward(d, u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy, dhT, ckpt, want_dh0=False):
+    """Raw backward.  Returns (du, dfl, dil, dB, dC, dD, dh0|None)."""
+    lib = _lib.load()
+    B, T, D = u.shape
+    N = Bm.shape[-1]
+    dev = u.device
+    du = torch.empty((B, T, D), dtype=u.dtype, device=dev)
+    dfl = torch.empty((B, T, D), dtype=f_logit.dtype, device=dev)
+    dil = torch.empty((B, T, D), dtype=f_logit.dtype, device=dev)
+    dB = torch.empty((B, T, N), dtype=Bm.dtype, device=dev)
+    dC = torch.empty((B, T, N), dtype=Bm.dtype, device=dev)
+    dD = torch.empty((D,), dtype=torch.float32, device=dev)
+    dh0 = torch.empty((B, D, N), dtype=torch.float32, device=dev) if want_dh0 else None
+    scratch = _workspace(lib.naju_b200_bwd_scratch_bytes(d), dev)
+    dy = dy.to(u.dtype).contiguous()
+    with torch.cuda.device(dev):
+        rc = lib.naju_b200_bwd(d, _ptr(u), _ptr(f_logit), _ptr(i_logit), _ptr(Bm), _ptr(Cm),
+                               _ptr(D_skip), _ptr(h0), _ptr(dy), _ptr(dhT), _ptr(ckpt), _ptr(du),
+                               _ptr(dfl), _ptr(dil), _ptr(dB), _ptr(dC), _ptr(dD), _ptr(dh0),
+                               _ptr(scratch), _stream())
+        _lib.check(rc, "naju_b200_bwd")
+        if _check_status_enabled() and B * T * D > 0:
+            st = lib.naju_b200_read_status(_ptr(scratch), _stream())
+            if st != 0:
+                raise RuntimeError(f"naju_b200_bwd device status {st} (bounded wait ran out)")
+    return du, dfl, dil, dB, dC, dD, dh0
+
+
+class _NajuB200Scan(torch.autograd.Function):
+    """Counterpart of _NajuCudaFn (naju/cuda/__init__.py:38-63) over the C ABI."""
+
+    @staticmethod
+    def forward(ctx, u, f_logit, i_logit, Bm, Cm, D_skip, h0, want_final):
+        in_dtypes = (u.dtype, f_logit.dtype, i_logit.dtype, Bm.dtype, Cm.dtype, D_skip.dtype)
+        pu, pf, pi, pB, pC, pD = _prepare(u, f_logit, i_logit, Bm, Cm, D_skip)
+        B, T, D = pu.shape
+        ph0 = _state_arg(h0, B, D, pB.shape[-1], "h0")
+        y, hT, _, ckpt, d = scan_forward(pu, pf, pi, pB, pC, pD, ph0, want_final=want_final)
+        ctx.save_for_backward(pu, pf, pi, pB, pC, pD, ph0, ckpt)
+        ctx.desc = d
+        ctx.in_dtypes = in_dtypes
+        ctx.h0_dtype = None if h0 is None else h0.dtype
+        ctx.want_final = want_final
+        if want_final:
+            return y, hT
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dhT=None):
+        pu, pf, pi, pB, pC, pD, ph0, ckpt = ctx.saved_tensors
+        B, T, D = pu.shape
+        N = pB.shape[-1]
+        if dy is None:
+            dy = torch.zeros_like(pu)
+        pdhT = _state_arg(dhT, B, D, N, "dhT") if (ctx.want_final and dhT is not None) else None
+        want_dh0 = ph0 is not None and ctx.needs_input_grad[6]
+        du, dfl, dil, dB, dC, dD, dh0 = scan_backward(ctx.desc, pu, pf, pi, pB, pC, pD, ph0, dy,
+                                                      pdhT, ckpt, want_dh0=want_dh0)
+        t = ctx.in_dtypes
+        return (du.to(t[0]), dfl.to(t[1]), dil.to(t[2]), dB.to(t[3]), dC.to(t[4]), dD.to(t[5]),
+                None if dh0 is None else dh0.to(ctx.h0_dtype), None)
+
+
+def naju_b200_scan(u, f_logit, i_logit, B, C, D_skip):
+    """Backend callable with the reference's 6-tensor signature (naju/scan.py:3-5)."""
+    return _NajuB200Scan.apply(u, f_logit, i_logit, B, C, D_skip, None, False)
+
+
+def naju_scan(u, f_logit, i_logit, B, C, D_skip, backend=None, *, h0=None,
+              return_final_state=False):
+    """y = scan(u, f_logit, i_logit, B, C, D_skip) — drop-in for naju/scan.py:75-76.
+
+    u, f_logit, i_logit [B,T,D]; B, C [B,T,N]; D_skip [D]; y [B,T,D] in u's dtype.
+    Differentiable w.r.t. all six tensors (and h0).  With return_final_state=True returns
+    (y, hT) where hT [B,D,N] fp32 is the state after the last step.
+    """
+    resolve_backend(backend)
+    out = _NajuB200Scan.apply(u, f_logit, i_logit, B, C, D_skip, h0, bool(return_final_state))
+    return out
+
+
+@torch.no_grad()
+def naju_scan_step(state, u_t, f_logit_t, i_logit_t, B_t, C_t, D_skip):
+    """Single-token decode update: one iteration of naju/scan.py:87-91.
+
+    state [B,D,N] fp32 (updated IN PLACE); u_t, f_logit_t, i_logit_t [B,D]; B_t, C_t [B,N].
+    Returns (y_t [B,D] in u_t's dtype, state).
+    """
+    lib = _lib.load()
+    if not state.is_cuda:
+        raise RuntimeError("naju_b200 step needs CUDA tensors (there is no CPU fallback)")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise RuntimeError("state must be a contiguous fp32 [B, D, N] tensor")
+    Bsz, D, N = state.shape
+    pu, pf, pi, pB, pC, pD = _prepare(u_t.unsqueeze(1), f_logit_t.unsqueeze(1),
+                                      i_logit_t.unsqueeze(1), B_t.unsqueeze(1), C_t.unsqueeze(1),
+                                      D_skip)
+    d = _desc(pu, pf, pi, pB, pC)
+    d.T = 1
+    d.u_sb, d.fl_sb, d.il_sb = max(d.u_sb, D), max(d.fl_sb, D), max(d.il_sb, D)
+    d.bm_sb, d.cm_sb = max(d.bm_sb, N), max(d.cm_sb, N)
+    y = torch.empty((Bsz, D), dtype=pu.dtype, device=state.device)
+    with torch.cuda.device(state.device):
+        rc = lib.naju_b200_step(d, _ptr(state), _ptr(pu), _ptr(pf), _ptr(pi), _ptr(pB), _ptr(pC),
+                                _ptr(pD), _ptr(y), _stream())
+    _lib.check(rc, "naju_b200_step")
+    return y, state

@@ -1,0 +1,193 @@
+"""GPU parity: the CUDA scan (through the Python host layer and the C ABI) against the
+reference's golden fixtures and the CPU oracle.
+
+Tolerances (relative L2 over the whole tensor, from the build target): forward output and
+final state 1e-3, gradients 2e-3.  The fp32 path is additionally held to a much tighter
+regression bound, because it computes the same recurrence in the same precision.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+TOL_FWD, TOL_GRAD = 1e-3, 2e-3          # build target
+TIGHT_FWD, TIGHT_GRAD = 2e-5, 1e-4      # fp32 regression bound
+GRADS = (("du", "u"), ("dfl", "fl"), ("dil", "il"), ("dB", "Bm"), ("dC", "Cm"), ("dD", "Dskip"))
+
+
+@pytest.fixture(autouse=True)
+def _status_checks(monkeypatch):
+    monkeypatch.setenv("NAJU_B200_CHECK_STATUS", "1")
+
+
+def _dev(d, dtype=torch.float32, gate_dtype=None, grad=True):
+    t = {}
+    for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "h0"):
+        if d.get(k) is None:
+            t[k] = None
+            continue
+        dt = torch.float32 if k in ("Dskip", "h0") else (gate_dtype or dtype) if k in ("fl", "il") else dtype
+        t[k] = torch.tensor(d[k], device="cuda").to(dt).requires_grad_(grad)
+    return t
+
+
+def _run(d, dtype=torch.float32, gate_dtype=None, state=False):
+    from naju_b200 import naju_scan
+    t = _dev(d, dtype, gate_dtype)
+    if state:
+        y, hT = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"], h0=t["h0"],
+                          return_final_state=True)
+        dhT = torch.tensor(d["dhT"], device="cuda")
+        torch.autograd.backward([y, hT], [torch.tensor(d["dy"], device="cuda").to(dtype), dhT])
+    else:
+        y = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"])
+        hT = None
+        y.backward(torch.tensor(d["dy"], device="cuda").to(dtype))
+    torch.cuda.synchronize()
+    out = dict(y=y.detach().float().cpu().numpy())
+    if hT is not None:
+        out["hT"] = hT.detach().cpu().numpy()
+        out["dh0"] = t["h0"].grad.float().cpu().numpy()
+    for g, k in GRADS:
+        out[g] = t[k].grad.float().cpu().numpy()
+    return out
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_fp32_matches_reference_fixture(name):
+    d, ref = load_golden(name)
+    out = _run(d, state="hT" in ref)
+    assert oracle.rel_l2(out["y"], ref["y"]) < TIGHT_FWD
+    if "hT" in ref:
+        assert oracle.rel_l2(out["hT"], ref["hT"]) < TIGHT_FWD
+        assert oracle.rel_l2(out["dh0"], ref["dh0"]) < TIGHT_GRAD
+    for g, _ in GRADS:
+        assert oracle.rel_l2(out[g], ref[g]) < TIGHT_GRAD, g
+
+
+SHAPES = [  # (B, T, D, N, f_shift) — multi-chunk, multi-channel-tile, ragged in T and D
+    (2, 1000, 384, 16, 2.0),
+    (1, 257, 200, 16, 4.0),
+    (3, 130, 136, 32, 2.0),
+    (1, 100, 260, 64, 2.0),
+    (1, 70, 72, 100, 2.0),
+    (1, 1, 8, 16, 2.0),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fp32_matches_oracle(shape):
+    B, T, D, N, fs = shape
+    d = oracle.make_inputs(B, T, D, N, seed=T + D, f_shift=fs, d_skip_scale=0.01, with_h0=True)
+    out = _run(d, state=True)
+    a = (d["u"], d["fl"], d["il"], d["Bm"], d["Cm"], d["Dskip"])
+    y, hT = oracle.oracle_fwd(*a, h0=d["h0"], return_final_state=True)
+    g = oracle.oracle_bwd(*a, d["dy"], h0=d["h0"], dhT=d["dhT"])
+    assert oracle.rel_l2(out["y"], y) < TIGHT_FWD
+    assert oracle.rel_l2(out["hT"], hT) < TIGHT_FWD
+    assert oracle.rel_l2(out["dh0"], g["dh0"]) < TIGHT_GRAD
+    for k, _ in GRADS:
+        assert oracle.rel_l2(out[k], g[k]) < TIGHT_GRAD, k
+
+
+def _round(a, dtype):
+    return torch.tensor(a).to(dtype).float().numpy()
+
+
+@pytest.mark.parametrize("dtype,gate_dtype", [(torch.bfloat16, None), (torch.bfloat16, torch.float32),
+                                               (torch.float16, None)])
+def test_low_precision_io_matches_identically_rounded_oracle(dtype, gate_dtype):
+    """Inputs are quantised once; the oracle runs in fp64 on the same quantised values and its
+    outputs are rounded the same way the kernel rounds them (the comparison
+    naju/tests/test_affine_chunk.py:142-169 makes for bf16 I/O)."""
+    B, T, D, N = 2, 300, 256, 16
+    d = oracle.make_inputs(B, T, D, N, seed=5, d_skip_scale=0.01)
+    q = dict(d)
+    for k in ("u", "Bm", "Cm", "dy"):
+        q[k] = _round(d[k], dtype)
+    for k in ("fl", "il"):
+        q[k] = _round(d[k], gate_dtype or dtype)
+    out = _run(q, dtype, gate_dtype)
+    a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
+    y = oracle.oracle_fwd(*a)
+    g = oracle.oracle_bwd(*a, q["dy"])
+    assert oracle.rel_l2(out["y"], _round(y, dtype)) < TOL_FWD
+    for k, src in GRADS:
+        gd = torch.float32 if k == "dD" else (gate_dtype or dtype) if k in ("dfl", "dil") else dtype
+        assert oracle.rel_l2(out[k], _round(g[k], gd)) < TOL_GRAD, k
+
+
+def test_strided_bc_views_and_no_grad():
+    """B and C arrive as two views of one [B,T,2N] tensor (naju/mixer.py:116)."""
+    from naju_b200 import naju_scan
+    B, T, D, N = 2, 150, 64, 16
+    d = oracle.make_inputs(B, T, D, N, seed=9)
+    bc = torch.tensor(np.concatenate([d["Bm"], d["Cm"]], -1), device="cuda")
+    Bm, Cm = torch.split(bc, [N, N], dim=-1)
+    with torch.no_grad():
+        y = naju_scan(torch.tensor(d["u"], device="cuda"), torch.tensor(d["fl"], device="cuda"),
+                      torch.tensor(d["il"], device="cuda"), Bm, Cm, torch.tensor(d["Dskip"], device="cuda"))
+    ref = oracle.oracle_fwd(d["u"], d["fl"], d["il"], d["Bm"], d["Cm"], d["Dskip"])
+    assert oracle.rel_l2(y.cpu().numpy(), ref) < TIGHT_FWD
+
+
+def test_transposed_u_layout():
+    """u arrives time-contiguous ([B,D,T] memory) from the mixer's conv (naju/mixer.py:115)."""
+    from naju_b200 import naju_scan
+    B, T, D, N = 1, 90, 40, 16
+    d = oracle.make_inputs(B, T, D, N, seed=13)
+    u = torch.tensor(d["u"], device="cuda").transpose(1, 2).contiguous().transpose(1, 2)
+    assert not u.is_contiguous()
+    y = naju_scan(u, torch.tensor(d["fl"], device="cuda"), torch.tensor(d["il"], device="cuda"),
+                  torch.tensor(d["Bm"], device="cuda"), torch.tensor(d["Cm"], device="cuda"),
+                  torch.tensor(d["Dskip"], device="cuda"))
+    ref = oracle.oracle_fwd(d["u"], d["fl"], d["il"], d["Bm"], d["Cm"], d["Dskip"])
+    assert oracle.rel_l2(y.cpu().numpy(), ref) < TIGHT_FWD
+
+
+def test_deterministic():
+    d = oracle.make_inputs(2, 200, 256, 16, seed=21)
+    a, b = _run(d), _run(d)
+    for k in a:
+        assert np.array_equal(a[k], b[k]), k
+
+
+def test_empty_time_axis():
+    from naju_b200 import naju_scan
+    h0 = torch.randn(2, 8, 16, device="cuda")
+    z = torch.zeros(2, 0, 8, device="cuda")
+    zn = torch.zeros(2, 0, 16, device="cuda")
+    y, hT = naju_scan(z, z, z, zn, zn, torch.zeros(8, device="cuda"), h0=h0, return_final_state=True)
+    assert y.shape == (2, 0, 8) and torch.equal(hT, h0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [16, 24, 64])
+def test_decode_step(dtype, N):
+    from naju_b200 import naju_scan_step
+    B, D = 5, 200
+    d = oracle.make_inputs(B, 1, D, N, seed=N, d_skip_scale=0.01, with_h0=True)
+    q = {k: (_round(d[k][:, 0], dtype) if k in ("u", "fl", "il", "Bm", "Cm") else d[k]) for k in d}
+    state = torch.tensor(d["h0"], device="cuda")
+    y, st = naju_scan_step(state, *(torch.tensor(q[k], device="cuda").to(dtype) for k in ("u", "fl", "il", "Bm", "Cm")),
+                           torch.tensor(d["Dskip"], device="cuda"))
+    yo, so = oracle.oracle_step(d["h0"], q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], d["Dskip"])
+    assert st.data_ptr() == state.data_ptr()
+    assert oracle.rel_l2(st.cpu().numpy(), so) < TIGHT_FWD
+    assert oracle.rel_l2(y.float().cpu().numpy(), _round(yo, dtype)) < (TIGHT_FWD if dtype == torch.float32 else TOL_FWD)
+
+
+def test_rejects_cpu_tensors_and_unknown_backend():
+    from naju_b200 import naju_scan
+    z = torch.zeros(1, 4, 8)
+    zn = torch.zeros(1, 4, 16)
+    with pytest.raises(RuntimeError):
+        naju_scan(z, z, z, zn, zn, torch.zeros(8))
+    with pytest.raises(ValueError):
+        naju_scan(z, z, z, zn, zn, torch.zeros(8), backend="nope")
