@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the gated-scan hot path: forward + backward scan throughput.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json's metric): B=8, T=16384, D=2048, N=16, bf16 inputs, fp32 state,
+synthetic seeded inputs u~N(0,1), f_logit~N(2,1), i_logit~N(0,1), B,C~N(0,1/N), dy~N(0,1).
+A step is one forward + one backward scan over that batch.  With N>1 GPUs every rank runs
+the same batch shape on its own data (batch sharding, no collective): weak scaling.
+
+Prints ONE JSON line on rank 0.  `value` is tokens/s with inputs resident in HBM; `e2e`
+is the same metric through the public `naju_scan` call with HOST buffers, host<->device
+copies inside the timed region.  `--impl reference` times the CPU restatement of the
+reference scan (oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "scan fwd+bwd tokens/sec and HBM GB/s % of peak, B=8 L=16K D=2048 N=16"
+CFG = dict(B=8, T=16384, D=2048, N=16)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(B, T, D, N, e=2):
+    """Per-launch algorithmic HBM bytes: forward reads u,fl,il,B,C and writes y;
+    backward reads u,fl,il,dy,B,C and writes du,dfl,dil,dB,dC."""
+    tok = B * T
+    return tok * (4 * D * e + 2 * N * e), tok * (7 * D * e + 4 * N * e)
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, f"/tmp/naju_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            # samples under load: the upper half of the sampled clocks
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_reference_run(steps, warmup, target_s=2.5):
+    """Times the CPU restatement of the reference scan (forward + backward, fp32) on all host
+    threads.  One step is a bounded sample of the metric workload: B=1, D=2048, N=16 and a
+    time length chosen so that a step takes about `target_s` seconds."""
+    import oracle
+    D, N = CFG["D"], CFG["N"]
+    cores = oracle.oracle_threads()
+
+    def one(T, seed=0):
+        d = oracle.make_inputs(1, T, D, N, seed=seed)
+        a = (d["u"], d["fl"], d["il"], d["Bm"], d["Cm"], d["Dskip"])
+        t0 = time.perf_counter()
+        oracle.oracle_fwd(*a, precision="f32")
+        oracle.oracle_bwd(*a, d["dy"], precision="f32")
+        return time.perf_counter() - t0
+
+    t_probe = one(64)
+    T = int(min(65536, max(64, 64 * target_s / max(t_probe, 1e-4))))
+    for _ in range(warmup):
+        one(T)
+    times = [one(T) for _ in range(steps)]
+    ms = 1e3 * sum(times) / len(times)
+    value = T / (ms / 1e3)
+    sample = f"B=1,T={T},D={D},N={N} fp32, {steps} steps after {warmup} warm-up"
+    return value, ms, cores, sample
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    value, ms, cores, sample = cpu_reference_run(args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "metric: scan fwd+bwd B=8 T=16384 D=2048 N=16 (bounded CPU sample)",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from naju_b200 import naju_scan
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback for the scan)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, T, D, N = CFG["B"], CFG["T"], CFG["D"], CFG["N"]
+    dt = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(rank)
+
+    def rn(*s):
+        return torch.randn(*s, device=dev, generator=g)
+
+    u = rn(B, T, D).to(dt)
+    fl = (rn(B, T, D) + 2.0).to(dt)
+    il = rn(B, T, D).to(dt)
+    Bm = (rn(B, T, N) / N ** 0.5).to(dt)
+    Cm = (rn(B, T, N) / N ** 0.5).to(dt)
+    Dk = torch.zeros(D, device=dev)
+    dy = rn(B, T, D).to(dt)
+    leaves = [u, fl, il, Bm, Cm, Dk]
+    for t in leaves:
+        t.requires_grad_(True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(ev=None):
+        for t in leaves:
+            t.grad = None
+        if ev:
+            ev[0].record()
+        y = naju_scan(u, fl, il, Bm, Cm, Dk)
+        if ev:
+            ev[1].record()
+        y.backward(dy)
+        if ev:
+            ev[2].record()
+        return y
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record()
+    for k in range(args.steps):
+        step(evs[k])
+    t_end.record()
+    barrier()
+    total_ms = t_begin.elapsed_time(t_end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+
+    # ---- end to end through the public call with HOST buffers
+    host_in = [t.detach().cpu().pin_memory() for t in (u, fl, il, Bm, Cm, dy)]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    host_out = None
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        nonlocal host_out
+        du_, dfl_, dil_, dB_, dC_, dy_ = [h.to(dev, non_blocking=True) for h in host_in]
+        ins = [du_, dfl_, dil_, dB_, dC_]
+        for t in ins:
+            t.requires_grad_(True)
+        Dl = Dk.detach().requires_grad_(True)
+        y = naju_scan(ins[0], ins[1], ins[2], ins[3], ins[4], Dl)
+        y.backward(dy_)
+        outs = [y.detach()] + [t.grad for t in ins] + [Dl.grad]
+        if host_out is None:
+            host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for h, o in zip(host_out, outs):
+            h.copy_(o, non_blocking=True)
+        return outs
+
+    e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([total_ms, e2e_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, fwd_ms, bwd_ms = times.tolist()
+
+    if rank == 0:
+        tokens = B * T * world
+        ms_per_step = total_ms / args.steps
+        value = tokens / (ms_per_step / 1e3)
+        fwd_bytes, bwd_bytes = algorithmic_bytes(B, T, D, N)
+        peak, peak_kind = measured_peak()
+        achieved = bwd_bytes / (bwd_ms / 1e3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "metric: scan fwd+bwd B=8 T=16384 D=2048 N=16 per GPU",
+                       "io_dtype": "bf16", "state_dtype": "f32", "sharding": f"batch x{world}, no collective",
+                       "l2": "inputs (4.3 GB per step) larger than L2",
+                       "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                       "fwd_gbs": fwd_bytes / (fwd_ms / 1e3) / 1e9,
+                       "fwd_bwd_gbs": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9,
+                       "fwd_bwd_frac_of_peak": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9 / peak},
+            "roofline": {"bound": "hbm", "kernel": "bwd_simt_kernel", "achieved": achieved,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "algorithmic_bytes_per_launch": bwd_bytes},
+            "e2e": {"value": B * T * world / (e2e_ms / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "steps": e2e_steps},
+            "gpu_launches": 5 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, ms, cores, sample = cpu_reference_run(3, 1, target_s=2.0)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,9 @@
 namespace naju {
 
 constexpr int kG = 8;  // time steps between two cross-warp partial-sum flushes
+// Below this retention the difference form of d f_logit loses more than ~3e-5 relative
+// accuracy (it matches the f_logit >= -5 envelope of naju/chunk_triton.py:200).
+constexpr float kDeepGate = 0.0078125f;
 
 template <typename TA, typename TG, int NS, int TC>
 __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
@@ -233,6 +236,50 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
         const float f = fg.s, w = ig.s * ut;
         const float4* Bt = reinterpret_cast<const float4*>(s_B + t * NS);
         const float4* Ct = reinterpret_cast<const float4*>(s_C + t * NS);
+        // Deep retention gate: r_t = f_t <xbar_t, x_{t-1}> is then far smaller than the two
+        // terms whose difference the recurrence forms, so it is computed directly instead,
+        // from x_{t-1} re-walked from the chunk-start state (rare; cost O(t) for this thread).
+        const bool deep = f < kDeepGate;
+        float r_exact = 0.f;
+        if (deep) {
+          float xp[NS];
+          if (c == 0) {
+#pragma unroll
+            for (int n = 0; n < NS; ++n)
+              xp[n] = (p.h0 != nullptr && d_ok && n < p.N) ? p.h0[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
+          } else {
+            const float4* src =
+                reinterpret_cast<const float4*>(p.ckS + ((tile - per_chunk) * kDT + tid) * NS);
+#pragma unroll
+            for (int q = 0; q < NS / 4; ++q) {
+              const float4 v = __ldg(src + q);
+              xp[4 * q] = v.x; xp[4 * q + 1] = v.y; xp[4 * q + 2] = v.z; xp[4 * q + 3] = v.w;
+            }
+          }
+          for (int tt = 0; tt < t; ++tt) {  // inputs of steps < t are still intact in smem
+            const float f2 = sigmoid_f(to_f32(s_fl[tt * kDT + tid]));
+            const float w2 = sigmoid_f(to_f32(s_il[tt * kDT + tid])) * to_f32(s_u[tt * kDT + tid]);
+            const float4* B2 = reinterpret_cast<const float4*>(s_B + tt * NS);
+#pragma unroll
+            for (int q = 0; q < NS / 4; ++q) {
+              const float4 bv = B2[q];
+              xp[4 * q + 0] = fmaf(f2, xp[4 * q + 0], w2 * bv.x);
+              xp[4 * q + 1] = fmaf(f2, xp[4 * q + 1], w2 * bv.y);
+              xp[4 * q + 2] = fmaf(f2, xp[4 * q + 2], w2 * bv.z);
+              xp[4 * q + 3] = fmaf(f2, xp[4 * q + 3], w2 * bv.w);
+            }
+          }
+          float dot = 0.f;
+#pragma unroll
+          for (int q = 0; q < NS / 4; ++q) {
+            const float4 cv = Ct[q];
+            dot = fmaf(fmaf(cv.x, dyt, carry[4 * q + 0]), xp[4 * q + 0], dot);
+            dot = fmaf(fmaf(cv.y, dyt, carry[4 * q + 1]), xp[4 * q + 1], dot);
+            dot = fmaf(fmaf(cv.z, dyt, carry[4 * q + 2]), xp[4 * q + 2], dot);
+            dot = fmaf(fmaf(cv.w, dyt, carry[4 * q + 3]), xp[4 * q + 3], dot);
+          }
+          r_exact = f * dot;
+        }
         float gsum = 0.f;
         float db[NS];
 #pragma unroll
@@ -253,6 +300,7 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
           carry[4 * q + 2] = f * dx2; carry[4 * q + 3] = f * dx3;
         }
         r += s_a[t * kDT + tid] - w * gsum;
+        if (deep) r = r_exact;
         s_u[t * kDT + tid] = from_f32<TA>(fmaf(ig.s, gsum, Dv * dyt));
         s_fl[t * kDT + tid] = from_f32<TG>(fg.one_minus * r);
         s_il[t * kDT + tid] = from_f32<TG>(gsum * w * ig.one_minus);
