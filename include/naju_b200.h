@@ -46,7 +46,14 @@ enum {
 /* device-side status bits, OR-ed into the workspace status word */
 enum {
   NAJU_ST_LOOKBACK_TIMEOUT = 1, /* a bounded wait on a neighbouring chunk's carry ran out */
-  NAJU_ST_BAD_TILE = 2          /* internal tile index out of range (never expected) */
+  NAJU_ST_BAD_TILE = 2,         /* internal tile index out of range (never expected) */
+  NAJU_ST_MMA_TIMEOUT = 4       /* a bounded wait on a tensor-core completion barrier ran out */
+};
+
+/* desc->flags */
+enum {
+  NAJU_FLAG_RECURRENT_ONLY = 1 /* always take the exact recurrent kernels, never the
+                                  tensor-core chunked form */
 };
 
 /* Problem description shared by forward and backward.
@@ -59,7 +66,7 @@ typedef struct naju_scan_desc {
   int32_t act_dtype;  /* u, y, dy, du            */
   int32_t gate_dtype; /* f_logit, i_logit, and their gradients */
   int32_t bc_dtype;   /* Bm, Cm, dB, dC          */
-  int32_t flags;      /* reserved, must be 0     */
+  int32_t flags;      /* NAJU_FLAG_* bits        */
   int64_t u_sb, u_st;
   int64_t fl_sb, fl_st;
   int64_t il_sb, il_st;

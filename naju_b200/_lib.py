@@ -14,6 +14,8 @@ ABI_VERSION = 1
 
 ST_LOOKBACK_TIMEOUT = 1
 ST_BAD_TILE = 2
+ST_MMA_TIMEOUT = 4
+FLAG_RECURRENT_ONLY = 1
 
 # every symbol include/naju_b200.h declares
 EXPORTS = ("naju_b200_version", "naju_b200_strerror", "naju_b200_chunk_len",

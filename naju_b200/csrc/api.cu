@@ -20,7 +20,7 @@ int check_desc(const naju_scan_desc* d, bool need_T) {
   if (d->B < 0 || d->D < 0 || d->N < 1 || d->N > 128 || (need_T && d->T < 0)) return NAJU_E_SHAPE;
   if (!dtype_ok(d->act_dtype) || !dtype_ok(d->gate_dtype) || !dtype_ok(d->bc_dtype)) return NAJU_E_DTYPE;
   if (!(d->gate_dtype == d->act_dtype || d->gate_dtype == NAJU_F32)) return NAJU_E_DTYPE;
-  if (d->flags != 0) return NAJU_E_SHAPE;
+  if ((d->flags & ~NAJU_FLAG_RECURRENT_ONLY) != 0) return NAJU_E_SHAPE;
   return NAJU_OK;
 }
 
@@ -126,6 +126,9 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   p.flags = reinterpret_cast<int*>(sc + sl.off_flags);
   p.aggP = reinterpret_cast<float*>(sc + sl.off_aggP);
   p.aggS = reinterpret_cast<float*>(sc + sl.off_aggS);
+  if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY) &&
+      fwd_tc_supported(g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype))
+    return launch_fwd_tc(p, g, desc->act_dtype, desc->gate_dtype, stream);
   return launch_fwd_simt(p, g, desc->act_dtype, desc->gate_dtype, stream);
 }
 

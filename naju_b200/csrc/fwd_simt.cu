@@ -14,8 +14,7 @@
 //           so every predecessor is already running; every wait is bounded.
 //   pass 2  scan again from the true carry-in, emitting y.
 // The inclusive chunk-end states double as the checkpoints the backward restarts from.
-#include "common.cuh"
-#include "params.h"
+#include "fwd_common.cuh"
 
 namespace naju {
 
@@ -32,21 +31,12 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const FwdParams p) {
   const int tid = threadIdx.x;
   if (tid == 0) s_ticket = atomicAdd(&p.hdr->ticket, 1u);
   __syncthreads();
-  const int64_t tile = s_ticket;
-  const int per_chunk = p.B * p.ndt;
-  const int c = static_cast<int>(tile / per_chunk);
-  const int rem = static_cast<int>(tile % per_chunk);
-  const int b = rem / p.ndt, dt = rem % p.ndt;
-  if (c >= p.nchunks) {  // cannot happen with grid == ntiles; recorded instead of trusted
-    if (tid == 0) atomicOr(&p.hdr->status, NAJU_ST_BAD_TILE);
+  TileCoord tc;
+  if (!decode_tile<TC>(s_ticket, p.B, p.T, p.D, p.nchunks, p.ndt, tid, tc)) {
+    if (tid == 0) atomicOr(&p.hdr->status, NAJU_ST_BAD_TILE);  // never expected
     return;
   }
-  const int t0 = c * TC;
-  const int len = min(TC, p.T - t0);
-  const int d0 = dt * kDT;
-  const int cols = min(kDT, p.D - d0);
-  const int d = d0 + tid;
-  const bool d_ok = d < p.D;
+  const int b = tc.b, t0 = tc.t0, len = tc.len, d0 = tc.d0, cols = tc.cols;
 
   // ---- stage the tile
   load_tile_async(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 * p.u_st + d0, p.u_st,
@@ -61,129 +51,13 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const FwdParams p) {
   cp_async_wait_all();
   __syncthreads();
 
-  // ---- pass 1: local scan from zero
-  float x[NS];
-#pragma unroll
-  for (int n = 0; n < NS; ++n) x[n] = 0.f;
-  float P = 1.f;
-  for (int t = 0; t < len; ++t) {
-    const float f = sigmoid_f(to_f32(s_fl[t * kDT + tid]));
-    const float w = sigmoid_f(to_f32(s_il[t * kDT + tid])) * to_f32(s_u[t * kDT + tid]);
-    P *= f;
-    const float4* Bt = reinterpret_cast<const float4*>(s_B + t * NS);
-#pragma unroll
-    for (int q = 0; q < NS / 4; ++q) {
-      const float4 bv = Bt[q];
-      x[4 * q + 0] = fmaf(f, x[4 * q + 0], w * bv.x);
-      x[4 * q + 1] = fmaf(f, x[4 * q + 1], w * bv.y);
-      x[4 * q + 2] = fmaf(f, x[4 * q + 2], w * bv.z);
-      x[4 * q + 3] = fmaf(f, x[4 * q + 3], w * bv.w);
-    }
-  }
-
-  // ---- carry-in by decoupled look-back
-  const int64_t slot = tile * kDT + tid;
-  float h[NS];
-  float Pin = 1.f;  // product of f from t=0 up to the start of this chunk
-  if (c == 0) {
-#pragma unroll
-    for (int n = 0; n < NS; ++n)
-      h[n] = (p.h0 != nullptr && d_ok && n < p.N) ? p.h0[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
-  } else {
-    p.aggP[slot] = P;
-    float4* dstS = reinterpret_cast<float4*>(p.aggS + slot * NS);
-#pragma unroll
-    for (int q = 0; q < NS / 4; ++q)
-      dstS[q] = make_float4(x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) st_release(p.flags + tile, 1);
-
-    float accP = 1.f;
-#pragma unroll
-    for (int n = 0; n < NS; ++n) h[n] = 0.f;
-    for (int j = c - 1; j >= 0; --j) {
-      const int64_t jt = static_cast<int64_t>(j) * per_chunk + rem;
-      const int64_t js = jt * kDT + tid;
-      const int st = wait_flag(p.flags + jt);
-      if (st == 0) {
-        atomicOr(&p.hdr->status, NAJU_ST_LOOKBACK_TIMEOUT);
-        break;
-      }
-      if (st == 2) {
-        const float4* src = reinterpret_cast<const float4*>(p.ckS + js * NS);
-#pragma unroll
-        for (int q = 0; q < NS / 4; ++q) {
-          const float4 v = __ldcg(src + q);
-          h[4 * q + 0] = fmaf(accP, v.x, h[4 * q + 0]);
-          h[4 * q + 1] = fmaf(accP, v.y, h[4 * q + 1]);
-          h[4 * q + 2] = fmaf(accP, v.z, h[4 * q + 2]);
-          h[4 * q + 3] = fmaf(accP, v.w, h[4 * q + 3]);
-        }
-        Pin = accP * __ldcg(p.ckP + js);
-        break;
-      }
-      const float4* src = reinterpret_cast<const float4*>(p.aggS + js * NS);
-#pragma unroll
-      for (int q = 0; q < NS / 4; ++q) {
-        const float4 v = __ldcg(src + q);
-        h[4 * q + 0] = fmaf(accP, v.x, h[4 * q + 0]);
-        h[4 * q + 1] = fmaf(accP, v.y, h[4 * q + 1]);
-        h[4 * q + 2] = fmaf(accP, v.z, h[4 * q + 2]);
-        h[4 * q + 3] = fmaf(accP, v.w, h[4 * q + 3]);
-      }
-      accP *= __ldcg(p.aggP + js);
-    }
-  }
-
-  // ---- publish the inclusive chunk-end state (also the backward's checkpoint)
-  {
-    float4* dstS = reinterpret_cast<float4*>(p.ckS + slot * NS);
-#pragma unroll
-    for (int q = 0; q < NS / 4; ++q)
-      dstS[q] = make_float4(fmaf(P, h[4 * q + 0], x[4 * q + 0]), fmaf(P, h[4 * q + 1], x[4 * q + 1]),
-                            fmaf(P, h[4 * q + 2], x[4 * q + 2]), fmaf(P, h[4 * q + 3], x[4 * q + 3]));
-    p.ckP[slot] = P * Pin;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) st_release(p.flags + tile, 2);
-  }
-
-  // ---- pass 2: scan from the true carry-in, emit y into the u tile
-  const float Dv = d_ok ? p.Dskip[d] : 0.f;
-#pragma unroll
-  for (int n = 0; n < NS; ++n) x[n] = h[n];
-  for (int t = 0; t < len; ++t) {
-    const float ut = to_f32(s_u[t * kDT + tid]);
-    const float f = sigmoid_f(to_f32(s_fl[t * kDT + tid]));
-    const float w = sigmoid_f(to_f32(s_il[t * kDT + tid])) * ut;
-    const float4* Bt = reinterpret_cast<const float4*>(s_B + t * NS);
-    const float4* Ct = reinterpret_cast<const float4*>(s_C + t * NS);
-    float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-    for (int q = 0; q < NS / 4; ++q) {
-      const float4 bv = Bt[q];
-      const float4 cv = Ct[q];
-      x[4 * q + 0] = fmaf(f, x[4 * q + 0], w * bv.x);
-      x[4 * q + 1] = fmaf(f, x[4 * q + 1], w * bv.y);
-      x[4 * q + 2] = fmaf(f, x[4 * q + 2], w * bv.z);
-      x[4 * q + 3] = fmaf(f, x[4 * q + 3], w * bv.w);
-      acc0 = fmaf(cv.x, x[4 * q + 0], acc0);
-      acc1 = fmaf(cv.y, x[4 * q + 1], acc1);
-      acc0 = fmaf(cv.z, x[4 * q + 2], acc0);
-      acc1 = fmaf(cv.w, x[4 * q + 3], acc1);
-    }
-    s_u[t * kDT + tid] = from_f32<TA>(fmaf(Dv, ut, acc0 + acc1));
-  }
-  if (c == p.nchunks - 1 && d_ok) {
-    if (p.hT != nullptr) {
-      float* o = p.hT + (static_cast<int64_t>(b) * p.D + d) * p.N;
-#pragma unroll
-      for (int n = 0; n < NS; ++n)
-        if (n < p.N) o[n] = x[n];
-    }
-    if (p.pT != nullptr) p.pT[static_cast<int64_t>(b) * p.D + d] = P * Pin;
-  }
+  float x[NS], h[NS];
+  float P, Pin;
+  tile_pass1<TA, TG, NS>(s_u, s_fl, s_il, s_B, len, tid, x, P);
+  carry_lookback<NS>(p, tc, tid, x, P, h, Pin);
+  const float Dv = tc.d_ok ? p.Dskip[tc.d] : 0.f;
+  tile_pass2<TA, TG, NS>(s_u, s_fl, s_il, s_B, s_C, len, tid, Dv, h);
+  write_final<NS>(p, tc, h, P * Pin);
   __syncthreads();
   store_tile(reinterpret_cast<TA*>(p.y) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d0, s_u,
              static_cast<int64_t>(p.D), len, cols, tid);

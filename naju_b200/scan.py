@@ -31,6 +31,16 @@ def resolve_backend(backend=None):
     return "b200"
 
 
+def _form():
+    """NAJU_B200_FORM selects the forward kernel family: "recurrent" (default) always takes the
+    exact recurrent kernels; "chunked" takes the tcgen05 tensor-core chunked form where it
+    applies (16-bit I/O, N <= 16) and the recurrent one elsewhere."""
+    f = os.environ.get("NAJU_B200_FORM", "recurrent").lower()
+    if f not in ("chunked", "recurrent"):
+        raise ValueError(f"NAJU_B200_FORM must be 'chunked' or 'recurrent', got {f!r}")
+    return f
+
+
 def _check_status_enabled():
     return os.environ.get("NAJU_B200_CHECK_STATUS", "0") == "1"
 
@@ -80,7 +90,7 @@ def _desc(u, f_logit, i_logit, Bm, Cm):
     d = _lib.ScanDesc()
     d.B, d.T, d.D, d.N = B, T, D, Bm.shape[-1]
     d.act_dtype, d.gate_dtype, d.bc_dtype = _DT[u.dtype], _DT[f_logit.dtype], _DT[Bm.dtype]
-    d.flags = 0
+    d.flags = _lib.FLAG_RECURRENT_ONLY if _form() == "recurrent" else 0
     d.u_sb, d.u_st = u.stride(0), u.stride(1)
     d.fl_sb, d.fl_st = f_logit.stride(0), f_logit.stride(1)
     d.il_sb, d.il_st = i_logit.stride(0), i_logit.stride(1)

@@ -123,6 +123,33 @@ def test_low_precision_io_matches_identically_rounded_oracle(dtype, gate_dtype):
         assert oracle.rel_l2(out[k], _round(g[k], gd)) < TOL_GRAD, k
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 128, 16, 2.0), (2, 1000, 384, 16, 2.0), (1, 700, 200, 12, 4.0),
+                                   (1, 300, 256, 16, -3.0), (1, 300, 256, 16, -12.0)])
+def test_tensor_core_chunked_forward(monkeypatch, shape):
+    """The tcgen05 chunked form against the fp64 oracle on the same bf16-quantised inputs.
+    Its arithmetic error is measured on the fp32 final state (tolerance 1e-3, the build
+    target).  y is emitted in bf16, so it is compared with the oracle rounded the same way;
+    a perturbation e before that rounding moves about e/ulp of the outputs by one bf16 ulp,
+    which bounds the distance by ~sqrt(e * 2^-8): 2e-3 here.  Deep-gate tiles (f_shift <= -3)
+    take the exact per-tile path and must meet the tight bound."""
+    from naju_b200 import naju_scan
+    monkeypatch.setenv("NAJU_B200_FORM", "chunked")
+    B, T, D, N, fs = shape
+    dt = torch.bfloat16
+    d = oracle.make_inputs(B, T, D, N, seed=3, f_shift=fs, d_skip_scale=0.01, with_h0=True)
+    q = {k: (_round(d[k], dt) if k in ("u", "fl", "il", "Bm", "Cm") else d[k]) for k in d}
+    t = {k: torch.tensor(q[k], device="cuda").to(dt if k in ("u", "fl", "il", "Bm", "Cm") else torch.float32)
+         for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "h0")}
+    with torch.no_grad():
+        y, hT = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"], h0=t["h0"],
+                          return_final_state=True)
+    yo, hTo = oracle.oracle_fwd(q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"], h0=q["h0"],
+                                return_final_state=True)
+    deep = fs <= -3.0
+    assert oracle.rel_l2(hT.cpu().numpy(), hTo) < (TIGHT_FWD if deep else TOL_FWD)
+    assert oracle.rel_l2(y.float().cpu().numpy(), _round(yo, dt)) < (TOL_FWD if deep else 2e-3)
+
+
 def test_strided_bc_views_and_no_grad():
     """B and C arrive as two views of one [B,T,2N] tensor (naju/mixer.py:116)."""
     from naju_b200 import naju_scan
