@@ -40,7 +40,8 @@ enum {
   NAJU_E_DTYPE = -3,     /* unsupported dtype combination */
   NAJU_E_STRIDE = -4,    /* inner stride not 1 / row stride smaller than the row */
   NAJU_E_WORKSPACE = -5, /* workspace too small or misaligned */
-  NAJU_E_ALIGN = -6      /* a pointer is not aligned to its element size */
+  NAJU_E_ALIGN = -6,     /* a pointer is not aligned to its element size */
+  NAJU_E_TOO_LARGE = -7  /* problem needs more workspace than naju_b200_fwd_noalloc() owns */
 };
 
 /* device-side status bits, OR-ed into the workspace status word */
@@ -129,6 +130,35 @@ int naju_b200_bwd(const naju_scan_desc* desc, const void* u, const void* f_logit
 int naju_b200_step(const naju_scan_desc* desc, float* state, const void* u, const void* f_logit,
                    const void* i_logit, const void* Bm, const void* Cm, const float* D_skip,
                    void* y, void* stream);
+
+/* Size of the built-in workspace of naju_b200_fwd_noalloc(): 32 MiB of device memory that
+ * every GPU loading this library holds until the process exits. */
+#define NAJU_B200_NOALLOC_BYTES (32u << 20)
+
+/* Forward scan for callers that cannot allocate device memory.  (No counterpart in the
+ * reference, whose native ops allocate their own outputs and checkpoints.)
+ *
+ * Meant for hosts that give a plugin only its input and output buffers and forbid allocation
+ * on that path -- an inference engine's enqueue hook, a serving loop that reserved its memory
+ * at start-up -- because cudaMalloc synchronises the device and can fail when memory is short.
+ * Same arguments and results as naju_b200_fwd() minus the two workspaces (and minus pT): they
+ * are carved out of a NAJU_B200_NOALLOC_BYTES array inside the library.  Nothing is allocated
+ * or freed by this call.
+ *   - Problems with naju_b200_ckpt_bytes() + naju_b200_fwd_scratch_bytes() above that size
+ *     are rejected with NAJU_E_TOO_LARGE (B*T*D up to about 15 M token-channels at
+ *     N <= 16 fits).
+ *   - The first call on each device looks the array's address up (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the array: calls that may overlap on the GPU (different
+ *     streams, or this and another thread) race on it and must be serialised by the caller.
+ *     The array keeps the previous call's contents; the call clears the part that has to
+ *     start at zero itself.
+ *   - The chunk-boundary states stay inside the library, so there is no matching backward:
+ *     use it for inference (prefill) only.
+ */
+int naju_b200_fwd_noalloc(const naju_scan_desc* desc, const void* u, const void* f_logit,
+                          const void* i_logit, const void* Bm, const void* Cm,
+                          const float* D_skip, const float* h0, void* y, float* hT, void* stream);
 
 /* Synchronises `stream` and returns the status word of a scratch buffer a forward or
  * backward call used (0 = clean; NAJU_ST_* bits otherwise), or a negative/positive error

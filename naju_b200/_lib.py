@@ -16,11 +16,14 @@ ST_LOOKBACK_TIMEOUT = 1
 ST_BAD_TILE = 2
 ST_MMA_TIMEOUT = 4
 FLAG_RECURRENT_ONLY = 1
+E_TOO_LARGE = -7
+NOALLOC_BYTES = 32 << 20
 
 # every symbol include/naju_b200.h declares
 EXPORTS = ("naju_b200_version", "naju_b200_strerror", "naju_b200_chunk_len",
            "naju_b200_ckpt_bytes", "naju_b200_fwd_scratch_bytes", "naju_b200_bwd_scratch_bytes",
-           "naju_b200_fwd", "naju_b200_bwd", "naju_b200_step", "naju_b200_read_status")
+           "naju_b200_fwd", "naju_b200_bwd", "naju_b200_step", "naju_b200_read_status",
+           "naju_b200_fwd_noalloc")
 
 
 class ScanDesc(ctypes.Structure):
@@ -65,6 +68,8 @@ def load():
     lib.naju_b200_bwd.argtypes = [dp] + [vp] * 19
     lib.naju_b200_step.restype = ctypes.c_int
     lib.naju_b200_step.argtypes = [dp] + [vp] * 9
+    lib.naju_b200_fwd_noalloc.restype = ctypes.c_int
+    lib.naju_b200_fwd_noalloc.argtypes = [dp] + [vp] * 10
     lib.naju_b200_read_status.restype = ctypes.c_int
     lib.naju_b200_read_status.argtypes = [vp, vp]
     if lib.naju_b200_version() != ABI_VERSION:

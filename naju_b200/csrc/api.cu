@@ -61,6 +61,9 @@ const char* naju_b200_strerror(int code) {
     case NAJU_E_STRIDE: return "unsupported strides (inner stride 1, row stride >= row length)";
     case NAJU_E_WORKSPACE: return "workspace missing or not 256-byte aligned";
     case NAJU_E_ALIGN: return "pointer not aligned to its element size";
+    case NAJU_E_TOO_LARGE:
+      return "problem too large for the built-in workspace of naju_b200_fwd_noalloc (32 MiB); "
+             "use naju_b200_fwd with caller-owned workspaces";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
   }
 }
