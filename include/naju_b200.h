@@ -89,6 +89,12 @@ int naju_b200_chunk_len(const naju_scan_desc* desc);
  * (the counterpart of the `ckpt` tensor of naju/cuda/naju_cuda.cu:45-46,246). */
 size_t naju_b200_ckpt_bytes(const naju_scan_desc* desc);
 
+/* Byte offset, inside the checkpoint buffer, of the cumulative retention products
+ * P[chunk][b][channel tile][128] fp32 (product of the retention gate from t=0 to the end of
+ * each chunk; padded channels included).  The chunk-end states [chunk][b][tile][128][NS] fp32
+ * start at offset 0, NS = N rounded up to 16, 32, 64 or 128. */
+size_t naju_b200_ckpt_decay_offset(const naju_scan_desc* desc);
+
 /* Bytes of transient scratch for one forward / one backward call. */
 size_t naju_b200_fwd_scratch_bytes(const naju_scan_desc* desc);
 size_t naju_b200_bwd_scratch_bytes(const naju_scan_desc* desc);

@@ -21,7 +21,7 @@ NOALLOC_BYTES = 32 << 20
 
 # every symbol include/naju_b200.h declares
 EXPORTS = ("naju_b200_version", "naju_b200_strerror", "naju_b200_chunk_len",
-           "naju_b200_ckpt_bytes", "naju_b200_fwd_scratch_bytes", "naju_b200_bwd_scratch_bytes",
+           "naju_b200_ckpt_bytes", "naju_b200_ckpt_decay_offset", "naju_b200_fwd_scratch_bytes", "naju_b200_bwd_scratch_bytes",
            "naju_b200_fwd", "naju_b200_bwd", "naju_b200_step", "naju_b200_read_status",
            "naju_b200_fwd_noalloc")
 
@@ -59,7 +59,7 @@ def load():
     lib.naju_b200_strerror.argtypes = [ctypes.c_int]
     lib.naju_b200_chunk_len.restype = ctypes.c_int
     lib.naju_b200_chunk_len.argtypes = [dp]
-    for name in ("naju_b200_ckpt_bytes", "naju_b200_fwd_scratch_bytes", "naju_b200_bwd_scratch_bytes"):
+    for name in ("naju_b200_ckpt_bytes", "naju_b200_ckpt_decay_offset", "naju_b200_fwd_scratch_bytes", "naju_b200_bwd_scratch_bytes"):
         getattr(lib, name).restype = ctypes.c_size_t
         getattr(lib, name).argtypes = [dp]
     lib.naju_b200_fwd.restype = ctypes.c_int

@@ -78,6 +78,11 @@ size_t naju_b200_ckpt_bytes(const naju_scan_desc* desc) {
   return ckpt_layout(make_geometry(*desc)).bytes;
 }
 
+size_t naju_b200_ckpt_decay_offset(const naju_scan_desc* desc) {
+  if (check_desc(desc, true) != NAJU_OK) return 0;
+  return ckpt_layout(make_geometry(*desc)).off_P;
+}
+
 size_t naju_b200_fwd_scratch_bytes(const naju_scan_desc* desc) {
   if (check_desc(desc, true) != NAJU_OK) return 0;
   return fwd_scratch_layout(make_geometry(*desc)).bytes;
