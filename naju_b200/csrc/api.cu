@@ -134,9 +134,12 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   p.flags = reinterpret_cast<int*>(sc + sl.off_flags);
   p.aggP = reinterpret_cast<float*>(sc + sl.off_aggP);
   p.aggS = reinterpret_cast<float*>(sc + sl.off_aggS);
-  if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY) &&
-      fwd_tc_supported(g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype))
-    return launch_fwd_tc(p, g, desc->act_dtype, desc->gate_dtype, stream);
+  if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY)) {
+    const int rc2 = launch_fwd_tc2(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
+    if (rc2 != -1000) return rc2;
+    if (fwd_tc_supported(g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype))
+      return launch_fwd_tc(p, g, desc->act_dtype, desc->gate_dtype, stream);
+  }
   return launch_fwd_simt(p, g, desc->act_dtype, desc->gate_dtype, stream);
 }
 

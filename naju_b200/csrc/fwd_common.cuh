@@ -60,7 +60,15 @@ __device__ __forceinline__ void tile_pass1(const TA* s_u, const TG* s_fl, const 
 // chunk, Pin = product of f from t=0 to the chunk start.  Publishes the aggregate, resolves
 // the carry-in by bounded decoupled look-back and publishes the inclusive chunk-end state
 // (the backward's checkpoint).  Must be called by all threads of the CTA.
-template <int NS>
+// NAMED = false: all threads of the CTA take part (__syncthreads).  NAMED = true: only the first
+// 128 threads do (named barrier 1), for kernels whose other warps have other roles.
+template <bool NAMED>
+__device__ __forceinline__ void carry_sync() {
+  if constexpr (NAMED) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else __syncthreads();
+}
+
+template <int NS, bool NAMED = false>
 __device__ __forceinline__ void carry_lookback(const FwdParams& p, const TileCoord& tc, int tid,
                                                const float (&S)[NS], float P, float (&h)[NS],
                                                float& Pin) {
@@ -77,9 +85,11 @@ __device__ __forceinline__ void carry_lookback(const FwdParams& p, const TileCoo
 #pragma unroll
     for (int q = 0; q < NS / 4; ++q)
       dstS[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) st_release(p.flags + tc.tile, 1);
+    carry_sync<NAMED>();
+    if (tid == 0) {
+      __threadfence();  // cumulative: orders every thread's stores above (seen through the barrier)
+      st_release(p.flags + tc.tile, 1);
+    }
 
     float accP = 1.f;
 #pragma unroll
@@ -114,9 +124,11 @@ __device__ __forceinline__ void carry_lookback(const FwdParams& p, const TileCoo
     dstS[q] = make_float4(fmaf(P, h[4 * q + 0], S[4 * q + 0]), fmaf(P, h[4 * q + 1], S[4 * q + 1]),
                           fmaf(P, h[4 * q + 2], S[4 * q + 2]), fmaf(P, h[4 * q + 3], S[4 * q + 3]));
   p.ckP[slot] = P * Pin;
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) st_release(p.flags + tc.tile, 2);
+  carry_sync<NAMED>();
+  if (tid == 0) {
+    __threadfence();
+    st_release(p.flags + tc.tile, 2);
+  }
 }
 
 // pass 2: scan from the true carry-in, y written into the u tile; x ends as the chunk-end state

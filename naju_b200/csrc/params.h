@@ -131,6 +131,9 @@ int launch_fwd_simt(const FwdParams& p, const Geometry& g, int act_dtype, int ga
                     void* stream);
 bool fwd_tc_supported(const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype);
 int launch_fwd_tc(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, void* stream);
+// TMA-fed persistent tensor-core forward; returns -1000 when the problem cannot take it
+int launch_fwd_tc2(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype,
+                   void* stream);
 int launch_bwd_simt(const BwdParams& p, const Geometry& g, int act_dtype, int gate_dtype,
                     void* dB, void* dC, float* dD, void* stream);
 int launch_step(const naju_scan_desc& d, float* state, const void* u, const void* fl,
