@@ -74,6 +74,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Asynchronous TMEM load: the registers are valid only after tmem_ld_wait16() on the same array.
+__device__ __forceinline__ void tmem_ld16_async(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Waits for every outstanding TMEM load of this thread; naming the registers keeps the compiler
+// from using them before the wait.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+
 // ---- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(count) : "memory");
@@ -85,7 +104,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
 }
-// bounded wait for the phase of parity `parity` to complete; false if the budget ran out
+// bounded wait for the phase of parity `parity` to complete; false if the budget ran out.
+// Waiters back off with nanosleep so that warps parked on a barrier do not take issue slots
+// from the warps doing the work.
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
   for (int it = 0; it < kSpinLimit; ++it) {
     uint32_t ok;
@@ -99,6 +120,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
         : "r"(mbar), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (it >= 2) __nanosleep(it < 16 ? 32 : 128);
   }
   return false;
 }
@@ -145,11 +167,24 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {  // lo -> 
 __device__ __forceinline__ float bf16lo_f32(uint32_t p) { return __uint_as_float(p << 16); }
 __device__ __forceinline__ float bf16hi_f32(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
 
-// Two-term bf16 split of a pair of floats: v = hi + lo with 16 mantissa bits kept.
+// Two-term bf16 split of a pair of floats: v ~= hi + lo with 16 mantissa bits kept.  Both terms
+// are truncations (the first one's error is exactly what the second term carries), so the split
+// costs only integer and FMA-pipe operations: the conversion instructions share the SFU pipe with
+// ex2/rcp, which is the busiest pipe of the gate warps.  Residual <= 2^-16 relative.
 __device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
-  hi = pack_bf16x2(a, b);
-  lo = pack_bf16x2(a - bf16lo_f32(hi), b - bf16hi_f32(hi));
+  const uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
+  const uint32_t ha = ua & 0xFFFF0000u, hb = ub & 0xFFFF0000u;
+  hi = __byte_perm(ha, hb, 0x7632);  // {hb[31:16], ha[31:16]}
+  const uint32_t la = __float_as_uint(a - __uint_as_float(ha)), lb = __float_as_uint(b - __uint_as_float(hb));
+  lo = __byte_perm(la, lb, 0x7632);
 }
+
+// shared-memory element -> fp32 without the conversion unit where the format allows it
+__device__ __forceinline__ float ld_as_f32(const __nv_bfloat16* p, int i) {
+  return __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(p)[i]) << 16);
+}
+__device__ __forceinline__ float ld_as_f32(const __half* p, int i) { return __half2float(p[i]); }
+__device__ __forceinline__ float ld_as_f32(const float* p, int i) { return p[i]; }
 
 // D(16x8, fp32) += A(16x16, bf16, row) . B(16x8, bf16, col)
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,

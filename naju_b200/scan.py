@@ -32,12 +32,12 @@ def resolve_backend(backend=None):
 
 
 def _form():
-    """NAJU_B200_FORM selects the forward kernel family: "recurrent" (default) always takes the
-    exact recurrent kernels; "chunked" takes the tcgen05 tensor-core chunked form where it
-    applies (16-bit I/O, N <= 16) and the recurrent one elsewhere."""
-    f = os.environ.get("NAJU_B200_FORM", "recurrent").lower()
-    if f not in ("chunked", "recurrent"):
-        raise ValueError(f"NAJU_B200_FORM must be 'chunked' or 'recurrent', got {f!r}")
+    """NAJU_B200_FORM selects the forward kernel family: "auto" (default) takes the tcgen05
+    tensor-core chunked form where it applies (16-bit activations, bf16 B/C, N == 16, TMA-legal
+    strides) and the exact recurrent kernels elsewhere; "recurrent" forces the recurrent ones."""
+    f = os.environ.get("NAJU_B200_FORM", "auto").lower()
+    if f not in ("auto", "chunked", "recurrent"):
+        raise ValueError(f"NAJU_B200_FORM must be 'auto', 'chunked' or 'recurrent', got {f!r}")
     return f
 
 

@@ -124,7 +124,9 @@ def test_low_precision_io_matches_identically_rounded_oracle(dtype, gate_dtype):
 
 
 @pytest.mark.parametrize("shape", [(2, 64, 128, 16, 2.0), (2, 1000, 384, 16, 2.0), (1, 700, 200, 12, 4.0),
-                                   (1, 300, 256, 16, -3.0), (1, 300, 256, 16, -12.0)])
+                                   (1, 300, 256, 16, -3.0), (1, 300, 256, 16, -12.0),
+                                   # enough channel tiles for the walk-along-time mode (ragged T)
+                                   (4, 520, 2432, 16, 2.0), (4, 520, 2432, 16, -2.5)])
 def test_tensor_core_chunked_forward(monkeypatch, shape):
     """The tcgen05 chunked form against the fp64 oracle on the same bf16-quantised inputs.
     Its arithmetic error is measured on the fp32 final state (tolerance 1e-3, the build
@@ -145,7 +147,7 @@ def test_tensor_core_chunked_forward(monkeypatch, shape):
                           return_final_state=True)
     yo, hTo = oracle.oracle_fwd(q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"], h0=q["h0"],
                                 return_final_state=True)
-    deep = fs <= -3.0
+    deep = fs <= -2.5
     assert oracle.rel_l2(hT.cpu().numpy(), hTo) < (TIGHT_FWD if deep else TOL_FWD)
     assert oracle.rel_l2(y.float().cpu().numpy(), _round(yo, dt)) < (TOL_FWD if deep else 2e-3)
 
