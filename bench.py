@@ -290,11 +290,11 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
                        "fwd_gbs": fwd_bytes / (fwd_ms / 1e3) / 1e9,
                        "fwd_bwd_gbs": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9,
                        "fwd_bwd_frac_of_peak": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9 / peak},
-            "roofline": {"bound": "hbm", "kernel": "bwd_simt_kernel", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "bwd_tc_kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None,
                          "algorithmic_bytes_per_launch": bwd_bytes},
-            "gpu_launches": 5 * args.steps,
+            "gpu_launches": 6 * args.steps,  # fwd_tc2 + bwd_tc + bwd_simt (stands down) + 3 finalize
             "clocks": clocks,
         }
         if e2e_steps:

@@ -48,7 +48,9 @@ enum {
 enum {
   NAJU_ST_LOOKBACK_TIMEOUT = 1, /* a bounded wait on a neighbouring chunk's carry ran out */
   NAJU_ST_BAD_TILE = 2,         /* internal tile index out of range (never expected) */
-  NAJU_ST_MMA_TIMEOUT = 4       /* a bounded wait on a tensor-core completion barrier ran out */
+  NAJU_ST_MMA_TIMEOUT = 4,      /* a bounded wait on a tensor-core completion barrier ran out */
+  NAJU_ST_DEEP_TILE = 8         /* the tensor-core backward met a deep-gate tile (never expected:
+                                   the forward routes such problems to the recurrent backward) */
 };
 
 /* desc->flags */

@@ -15,6 +15,7 @@ ABI_VERSION = 1
 ST_LOOKBACK_TIMEOUT = 1
 ST_BAD_TILE = 2
 ST_MMA_TIMEOUT = 4
+ST_DEEP_TILE = 8
 FLAG_RECURRENT_ONLY = 1
 E_TOO_LARGE = -7
 NOALLOC_BYTES = 32 << 20

@@ -123,6 +123,8 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   char* sc = static_cast<char*>(scratch);
   cudaError_t e = cudaMemsetAsync(sc, 0, sl.zero_bytes, st);
   if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemsetAsync(ck + cl.off_trailer, 0, 256, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
 
   FwdParams p;
   fill_common(p, desc, g);
@@ -130,6 +132,7 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   p.y = y; p.hT = hT; p.pT = pT;
   p.ckS = reinterpret_cast<float*>(ck + cl.off_S);
   p.ckP = reinterpret_cast<float*>(ck + cl.off_P);
+  p.fwd_form = reinterpret_cast<int*>(ck + cl.off_trailer);
   p.hdr = reinterpret_cast<ScratchHeader*>(sc);
   p.flags = reinterpret_cast<int*>(sc + sl.off_flags);
   p.aggP = reinterpret_cast<float*>(sc + sl.off_aggP);
@@ -186,6 +189,16 @@ int naju_b200_bwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   p.dBpart = reinterpret_cast<float*>(sc + sl.off_dBpart);
   p.dCpart = reinterpret_cast<float*>(sc + sl.off_dCpart);
   p.dDpart = reinterpret_cast<float*>(sc + sl.off_dDpart);
+  p.fwd_form = reinterpret_cast<const int*>(ck + cl.off_trailer);
+  p.tc_launched = 0;
+  if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY)) {
+    // The tensor-core backward stands down on the device unless the forward of these inputs ran
+    // chunked and met no deep-gate tile; the recurrent backward launched after it does the
+    // opposite, so exactly one of the two does the work and no host round trip is needed.
+    const int rc2 = launch_bwd_tc(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, p.fwd_form, stream);
+    if (rc2 == 0) p.tc_launched = 1;
+    else if (rc2 != -1000) return rc2;
+  }
   return launch_bwd_simt(p, g, desc->act_dtype, desc->gate_dtype, dB, dC, dD, stream);
 }
 

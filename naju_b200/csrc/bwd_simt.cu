@@ -39,6 +39,9 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
   float* s_part = s_a + TC * kDT;                           // [kWarps][kG][NS]
   __shared__ unsigned int s_ticket;
 
+  // the tensor-core backward was launched for this call and is doing the work
+  if (p.tc_launched && (*p.fwd_form & 3) == 1) return;
+
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_ticket = atomicAdd(&p.hdr->ticket, 1u);
   __syncthreads();
@@ -344,8 +347,10 @@ __global__ void finalize_bc_kernel(const float* __restrict__ part, void* __restr
 
 // dD[d] = sum_rows part[row][d]; block = 32 channels x 32 row lanes, fixed-order tree
 __global__ void finalize_dD_kernel(const float* __restrict__ part, float* __restrict__ dD,
-                                   int rows, int ld, int D) {
+                                   int rows, int rows_tc, const int* __restrict__ fwd_form, int ld, int D) {
   __shared__ float red[32][33];
+  // the tensor-core backward writes one partial row per batch row, the recurrent one per chunk
+  if (rows_tc > 0 && (*fwd_form & 3) == 1) rows = rows_tc;
   const int dl = threadIdx.x, rl = threadIdx.y;
   const int d = blockIdx.x * 32 + dl;
   float s = 0.f;
@@ -403,6 +408,7 @@ int launch_bwd_simt(const BwdParams& p, const Geometry& g, int act, int gate, vo
   finalize_bc_kernel<<<blocks, 256, 0, st>>>(p.dBpart, dB, rows, g.ndt, g.NS, g.N, p.bc_dtype);
   finalize_bc_kernel<<<blocks, 256, 0, st>>>(p.dCpart, dC, rows, g.ndt, g.NS, g.N, p.bc_dtype);
   finalize_dD_kernel<<<(g.D + 31) / 32, dim3(32, 32), 0, st>>>(p.dDpart, dD, g.nchunks * g.B,
+                                                              p.tc_launched ? g.B : 0, p.fwd_form,
                                                               g.ndt * kDT, g.D);
   return static_cast<int>(cudaGetLastError());
 }

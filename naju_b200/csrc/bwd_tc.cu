@@ -1,0 +1,682 @@
+// Backward gated scan, chunked (state-expansion) form on tcgen05 tensor cores.
+//
+// One persistent CTA per channel tile (one batch row x 128 channels) walks the chunks of Q = 64
+// steps in REVERSE time; the adjoint carry stays in registers, the state entering each chunk
+// comes from the checkpoints the forward saved.  Per chunk and channel d, with P_t = prod f,
+// R_t = 1/P_t, wt_s = w_s R_s (w = sigmoid(i_logit) u), al_t = dy_t P_t, h the state entering
+// the chunk, lam the adjoint entering it from the future, lt = P_Q lam and G = tril(C B^T):
+//
+//   Yt[d,t] = sum_{s<=t} G[t,s] wt[d,s] + <C_t, h[d]>            (forward readout / P_t)
+//   gt[d,s] = sum_{t>=s} G[t,s] al[d,t] + <B_s, lt[d]>           (g_s / R_s, g = <xbar, B>)
+//   dL[d,n] = sum_t al[d,t] C[t,n]                               (adjoint leaving the chunk - P_Q lam)
+//   M2[t,s] = sum_d al[d,t] wt[d,s],  U[t,n] = sum_d al[d,t] h[d,n],  V[s,n] = sum_d wt[d,s] lt[d,n]
+//   dC[t,n] = U[t,n] + sum_{s<=t} M2[t,s] B[s,n]      dB[s,n] = V[s,n] + sum_{t>=s} M2[t,s] C[t,n]
+//
+// (the adjoint of naju/scan.py:79-93 as written out in naju/cuda/naju_cuda.cu:85-144; the Gram
+// form of dB/dC is the one naju/chunk_bwd_triton.py:20-99 uses on 16-step blocks).  Then
+//   r_t = r_{t+1} + al_t Yt_t - wt_t gt_t  (r at the chunk end = <lam, x_end>),
+//   d f_logit = (1-f_t) r_t,  du = (i_t R_t) gt_t + D_skip dy_t,  d i_logit = wt_t (1-i_t) gt_t.
+// All seven contractions are tcgen05.mma (kind::f16, bf16 operands in two-term splits, fp32
+// accumulators in TMEM, M = 128).  Each channel owns one row [al | wt | h | lt] in shared memory;
+// the same bytes serve as K-major operands for the per-channel GEMMs (contraction over time or
+// state) and as MN-major operands for the cross-channel ones (contraction over the 128 channels),
+// and the G buffer serves K-major for Yt and MN-major (i.e. transposed) for gt.
+//
+// Warps: 0-3 thread = channel (gates -> operand rows and per-step coefficients into TMEM; after
+// the MMAs the reverse-time epilogue), 4 TMA producer, 5 shared-operand builder (mma.sync),
+// 6 MMA issuer.  Every wait is bounded.  Tiles with deep retention gates (prod f < 2^-80 in a
+// chunk) cannot be factorised; the forward records whether it met one, and this kernel stands
+// down in that case (the exact recurrent backward runs instead).
+#include <algorithm>
+#include <type_traits>
+
+#include "common.cuh"
+#include "params.h"
+#include "tc_common.cuh"
+
+namespace naju {
+namespace tcb {
+
+using namespace tcx;
+
+constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, RING = 3;
+constexpr int NMAIN = 128, NTHREADS = 224;
+// channel row (bf16, chunks of 8): [al1 8 | w1 8 | h1 2 | l1 2 | al2 8 | w2 8 | h2 2 | l2 2]
+constexpr int R_A1 = 0, R_W1 = 8, R_H1 = 16, R_L1 = 18, R_A2 = 20, R_W2 = 28, R_H2 = 36, R_L2 = 38, R_CH = 40;
+constexpr uint32_t SBO_R = R_CH * 128, ROWS_BYTES = 16 * SBO_R;  // 81920
+// BG rows t: [C 2 | g1 8 | g2 8]
+constexpr int BG_C = 0, BG_G1 = 2, BG_G2 = 10;
+constexpr uint32_t SBO_BG = 18 * 128, BG_BYTES = 8 * SBO_BG;     // 18432
+constexpr uint32_t SBO_BB = 2 * 128, BB_BYTES = 8 * SBO_BB;      // rows s: [B 2]        2048
+constexpr uint32_t SBO_T = 8 * 128, T_BYTES = 2 * SBO_T;         // rows n: [X^T 8]      2048 (CT and BT)
+// M2 operand rows t: [m1 8 | m2 8]; 64 real rows, addressed as 128 (the rest is never used)
+constexpr int M_1 = 0, M_2 = 8;
+constexpr uint32_t SBO_M = 16 * 128, M_BYTES = 8 * SBO_M;        // 16384
+constexpr uint32_t BC_BYTES = Q * NS * 2;
+// TMEM columns
+constexpr uint32_t TM_Y = 0, TM_G = 64, TM_DL = 128, TM_X = 144, TM_DCI = 240, TM_CF = 256, TM_CI = 320,
+                   TM_CU = 384, TM_DBI = 448, TMEM_COLS = 512;
+constexpr float kRMax = 1.0e24f;
+constexpr float kNegLog2e = -1.4426950408889634f;
+
+__device__ __forceinline__ float fast_ex2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// MN-major no-swizzle descriptor: `kgroup` = bytes between groups of 8 along K (LBO field),
+// `mnchunk` = bytes between 8-element chunks along M/N (SBO field).
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t saddr, uint32_t kgroup, uint32_t mnchunk) {
+  return umma_desc(saddr, kgroup, mnchunk);
+}
+__device__ __forceinline__ uint32_t idesc_bf16(int N, uint32_t a_mn, uint32_t b_mn) {
+  return umma_idesc(128, N, 1) | (a_mn << 15) | (b_mn << 16);
+}
+
+struct Maps {
+  CUtensorMap u, fl, il, dy, bm, cm;
+};
+
+struct Smem {
+  static constexpr uint32_t slab_bytes = SLAB * kDT * 2 * 4;  // u, fl, il, dy (all 16-bit)
+  static constexpr uint32_t off_ring = 0;
+  static constexpr uint32_t off_rows = off_ring + RING * slab_bytes;
+  static constexpr uint32_t off_BG = off_rows + ROWS_BYTES;
+  static constexpr uint32_t off_BB = off_BG + BG_BYTES;
+  static constexpr uint32_t off_CT = off_BB + BB_BYTES;
+  static constexpr uint32_t off_BT = off_CT + T_BYTES;
+  static constexpr uint32_t off_M = off_BT + T_BYTES;
+  static constexpr uint32_t off_bc = off_M + M_BYTES;           // [2 tiles][B raw | C raw]
+  static constexpr uint32_t off_out = off_bc + 2 * 2 * BC_BYTES;  // du | dfl | dil, [64][128] each
+  static constexpr uint32_t total = off_out + 3 * Q * kDT * 2;
+};
+
+struct Bars {
+  unsigned long long full[RING], empty[RING];
+  unsigned long long bc_full[2], bc_empty[2];
+  unsigned long long rows_full, ops_full, d_full, m2_full, d5_full, tile_done;
+};
+
+template <typename TA>
+__global__ void __launch_bounds__(NTHREADS, 1)
+bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* __restrict__ fwd_form) {
+  (void)0;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ Bars bars;
+  __shared__ unsigned int s_tmem;
+
+  // stand down unless the forward ran in the chunked form and met no deep-gate tile
+  if ((*fwd_form & 3) != 1) return;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t sbase = smem_u32(smem);
+  const int b = static_cast<int>(blockIdx.x) / p.ndt, dt = static_cast<int>(blockIdx.x) % p.ndt;
+  const int d0 = dt * kDT;
+  const int per_chunk = p.B * p.ndt;
+  const int nchunks = p.nchunks;
+
+  if (tid == 0) {
+    for (int i = 0; i < RING; ++i) {
+      mbar_init(smem_u32(&bars.full[i]), 1);
+      mbar_init(smem_u32(&bars.empty[i]), NMAIN);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&bars.bc_full[i]), 1);
+      mbar_init(smem_u32(&bars.bc_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&bars.rows_full), NMAIN);
+    mbar_init(smem_u32(&bars.ops_full), 1);
+    mbar_init(smem_u32(&bars.d_full), 1);
+    mbar_init(smem_u32(&bars.m2_full), NMAIN);
+    mbar_init(smem_u32(&bars.d5_full), 1);
+    mbar_init(smem_u32(&bars.tile_done), NMAIN);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
+  // zero the operand buffers once: the upper triangle of g1/g2 and of the M2 operand, and the
+  // unused M2 rows, are never written afterwards
+  for (uint32_t i = tid * 16; i < Smem::off_bc - Smem::off_BG; i += NTHREADS * 16)
+    *reinterpret_cast<uint4*>(smem + Smem::off_BG + i) = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
+
+  if (warp == 4) {
+    // ===================================================================== TMA producer
+    if (lane == 0) {
+      uint32_t slab = 0;
+      for (int it = 0; it < nchunks; ++it) {
+        const int c = nchunks - 1 - it, t0 = c * Q, par = it & 1;
+        if (it >= 2 && !mbar_wait(smem_u32(&bars.bc_empty[par]), ((it >> 1) & 1) ^ 1)) timeout();
+        {
+          const uint32_t bar = smem_u32(&bars.bc_full[par]);
+          const uint32_t dst = sbase + Smem::off_bc + par * 2 * BC_BYTES;
+          mbar_arrive_expect_tx(bar, 2 * BC_BYTES);
+          tma_load_3d(dst, &maps.bm, 0, t0, b, bar);
+          tma_load_3d(dst + BC_BYTES, &maps.cm, 0, t0, b, bar);
+        }
+        for (int k = 0; k < NSLAB; ++k, ++slab) {
+          const uint32_t slot = slab % RING, ph = (slab / RING) & 1;
+          if (slab >= RING && !mbar_wait(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
+          const uint32_t bar = smem_u32(&bars.full[slot]);
+          const uint32_t dst = sbase + Smem::off_ring + slot * Smem::slab_bytes;
+          mbar_arrive_expect_tx(bar, Smem::slab_bytes);
+          tma_load_3d(dst, &maps.u, d0, t0 + k * SLAB, b, bar);
+          tma_load_3d(dst + SLAB * kDT * 2, &maps.fl, d0, t0 + k * SLAB, b, bar);
+          tma_load_3d(dst + SLAB * kDT * 4, &maps.il, d0, t0 + k * SLAB, b, bar);
+          tma_load_3d(dst + SLAB * kDT * 6, &maps.dy, d0, t0 + k * SLAB, b, bar);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ===================================================================== operand builder
+    const int g = lane >> 2, t4 = lane & 3;
+    unsigned char* s_BG = smem + Smem::off_BG;
+    unsigned char* s_BB = smem + Smem::off_BB;
+    unsigned char* s_CT = smem + Smem::off_CT;
+    unsigned char* s_BT = smem + Smem::off_BT;
+    for (int it = 0; it < nchunks; ++it) {
+      const int par = it & 1;
+      if (!mbar_wait(smem_u32(&bars.bc_full[par]), (it >> 1) & 1)) timeout();
+      // the previous tile's MMAs (and its last reads of these buffers) must be over
+      if (it >= 1 && !mbar_wait(smem_u32(&bars.tile_done), (it - 1) & 1)) timeout();
+      const __nv_bfloat16* Braw = reinterpret_cast<const __nv_bfloat16*>(smem + Smem::off_bc + par * 2 * BC_BYTES);
+      const __nv_bfloat16* Craw = Braw + Q * NS;
+      for (int e = lane; e < Q * 2; e += 32) {  // C into BG, B into BB: rows of 32 bytes
+        const int t = e >> 1, half = e & 1;
+        *reinterpret_cast<uint4*>(s_BG + op_off16(t, BG_C * 8 + half * 8, SBO_BG)) =
+            *reinterpret_cast<const uint4*>(Craw + t * NS + half * 8);
+        *reinterpret_cast<uint4*>(s_BB + op_off16(t, half * 8, SBO_BB)) =
+            *reinterpret_cast<const uint4*>(Braw + t * NS + half * 8);
+      }
+      for (int e = lane; e < NS * (Q / 8); e += 32) {  // C^T and B^T: (row n, eight columns t)
+        const int n = e % NS, s8 = e / NS;
+        uint32_t wc[4], wb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r0 = (8 * s8 + 2 * j) * NS + n, r1 = r0 + NS;
+          wc[j] = static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Craw)[r0]) |
+                  (static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Craw)[r1]) << 16);
+          wb[j] = static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Braw)[r0]) |
+                  (static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Braw)[r1]) << 16);
+        }
+        *reinterpret_cast<uint4*>(s_CT + op_off16(n, 8 * s8, SBO_T)) = make_uint4(wc[0], wc[1], wc[2], wc[3]);
+        *reinterpret_cast<uint4*>(s_BT + op_off16(n, 8 * s8, SBO_T)) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+      }
+#pragma unroll 1
+      for (int mt = 0; mt < Q / 16; ++mt) {  // G = tril(C B^T), two bf16 terms
+        const int r0 = 16 * mt + g, r1 = r0 + 8;
+        const uint32_t a0 = *reinterpret_cast<const uint32_t*>(Craw + r0 * NS + 2 * t4);
+        const uint32_t a1 = *reinterpret_cast<const uint32_t*>(Craw + r1 * NS + 2 * t4);
+        const uint32_t a2 = *reinterpret_cast<const uint32_t*>(Craw + r0 * NS + 2 * t4 + 8);
+        const uint32_t a3 = *reinterpret_cast<const uint32_t*>(Craw + r1 * NS + 2 * t4 + 8);
+        for (int nt = 0; nt <= 2 * mt + 1; ++nt) {
+          float c[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Braw + (8 * nt + g) * NS + 2 * t4);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Braw + (8 * nt + g) * NS + 2 * t4 + 8);
+          mma_bf16_16x8x16(c, a0, a1, a2, a3, b0, b1);
+          const int s0 = 8 * nt + 2 * t4;
+          uint32_t hi, lo;
+          split_bf16x2(s0 <= r0 ? c[0] : 0.f, s0 + 1 <= r0 ? c[1] : 0.f, hi, lo);
+          *reinterpret_cast<uint32_t*>(s_BG + op_off16(r0, BG_G1 * 8 + s0, SBO_BG)) = hi;
+          *reinterpret_cast<uint32_t*>(s_BG + op_off16(r0, BG_G2 * 8 + s0, SBO_BG)) = lo;
+          split_bf16x2(s0 <= r1 ? c[2] : 0.f, s0 + 1 <= r1 ? c[3] : 0.f, hi, lo);
+          *reinterpret_cast<uint32_t*>(s_BG + op_off16(r1, BG_G1 * 8 + s0, SBO_BG)) = hi;
+          *reinterpret_cast<uint32_t*>(s_BG + op_off16(r1, BG_G2 * 8 + s0, SBO_BG)) = lo;
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&bars.ops_full));
+        mbar_arrive(smem_u32(&bars.bc_empty[par]));
+      }
+    }
+  } else if (warp == 6) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      const uint32_t aR = sbase + Smem::off_rows, aBG = sbase + Smem::off_BG, aBB = sbase + Smem::off_BB;
+      const uint32_t aCT = sbase + Smem::off_CT, aBT = sbase + Smem::off_BT, aM = sbase + Smem::off_M;
+      const uint32_t iKK64 = idesc_bf16(64, 0, 0), iKM64 = idesc_bf16(64, 0, 1), iKK16 = idesc_bf16(16, 0, 0);
+      const uint32_t iMM96 = idesc_bf16(96, 1, 1), iMK16 = idesc_bf16(16, 1, 0);
+      auto rowK = [&](int chunk) { return umma_desc(aR + chunk * 128, 128, SBO_R); };  // K-major channel rows
+      for (int it = 0; it < nchunks; ++it) {
+        const uint32_t par = it & 1;
+        if (!mbar_wait(smem_u32(&bars.rows_full), par)) timeout();
+        if (!mbar_wait(smem_u32(&bars.ops_full), par)) timeout();
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          // Yt += w1.g1 + w1.g2 + w2.g1   (K = s)
+          const uint64_t g1 = umma_desc(aBG + (BG_G1 + 2 * ks) * 128, 128, SBO_BG);
+          const uint64_t g2 = umma_desc(aBG + (BG_G2 + 2 * ks) * 128, 128, SBO_BG);
+          umma_bf16(tmem + TM_Y, rowK(R_W1 + 2 * ks), g1, iKK64, ks > 0);
+          umma_bf16(tmem + TM_Y, rowK(R_W1 + 2 * ks), g2, iKK64, 1u);
+          umma_bf16(tmem + TM_Y, rowK(R_W2 + 2 * ks), g1, iKK64, 1u);
+          // gt += al1.g1^T + al1.g2^T + al2.g1^T   (K = t: the G buffer read MN-major)
+          const uint64_t g1t = umma_desc_mn(aBG + 2 * ks * SBO_BG + BG_G1 * 128, SBO_BG, 128);
+          const uint64_t g2t = umma_desc_mn(aBG + 2 * ks * SBO_BG + BG_G2 * 128, SBO_BG, 128);
+          umma_bf16(tmem + TM_G, rowK(R_A1 + 2 * ks), g1t, iKM64, ks > 0);
+          umma_bf16(tmem + TM_G, rowK(R_A1 + 2 * ks), g2t, iKM64, 1u);
+          umma_bf16(tmem + TM_G, rowK(R_A2 + 2 * ks), g1t, iKM64, 1u);
+          // dL += al1.C + al2.C   (K = t, B operand = C^T rows)
+          const uint64_t ct = umma_desc(aCT + 2 * ks * 128, 128, SBO_T);
+          umma_bf16(tmem + TM_DL, rowK(R_A1 + 2 * ks), ct, iKK16, ks > 0);
+          umma_bf16(tmem + TM_DL, rowK(R_A2 + 2 * ks), ct, iKK16, 1u);
+        }
+        {  // Yt += (h1 + h2).C,  gt += (l1 + l2).B   (K = n)
+          const uint64_t cc = umma_desc(aBG + BG_C * 128, 128, SBO_BG), bb = umma_desc(aBB, 128, SBO_BB);
+          umma_bf16(tmem + TM_Y, rowK(R_H1), cc, iKK64, 1u);
+          umma_bf16(tmem + TM_Y, rowK(R_H2), cc, iKK64, 1u);
+          umma_bf16(tmem + TM_G, rowK(R_L1), bb, iKK64, 1u);
+          umma_bf16(tmem + TM_G, rowK(R_L2), bb, iKK64, 1u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // cross-channel: X[m, n'] += [al | wt]^T . [wt | h | lt]   (K = 16 channels per step)
+          const uint32_t grp = aR + 2 * ks * SBO_R;
+          const uint64_t A1 = umma_desc_mn(grp + R_A1 * 128, SBO_R, 128), A2 = umma_desc_mn(grp + R_A2 * 128, SBO_R, 128);
+          const uint64_t B1 = umma_desc_mn(grp + R_W1 * 128, SBO_R, 128), B2 = umma_desc_mn(grp + R_W2 * 128, SBO_R, 128);
+          umma_bf16(tmem + TM_X, A1, B1, iMM96, ks > 0);
+          umma_bf16(tmem + TM_X, A1, B2, iMM96, 1u);
+          umma_bf16(tmem + TM_X, A2, B1, iMM96, 1u);
+        }
+        umma_commit(smem_u32(&bars.d_full));
+        // second round: the intra-chunk parts of dC and dB from the masked M2 the main warps wrote
+        if (!mbar_wait(smem_u32(&bars.m2_full), par)) timeout();
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t bt = umma_desc(aBT + 2 * ks * 128, 128, SBO_T), ct = umma_desc(aCT + 2 * ks * 128, 128, SBO_T);
+          // dCi[t,n] += sum_s M2[t,s] B[s,n]    (A = M2 rows, K = s)
+          umma_bf16(tmem + TM_DCI, umma_desc(aM + (M_1 + 2 * ks) * 128, 128, SBO_M), bt, iKK16, ks > 0);
+          umma_bf16(tmem + TM_DCI, umma_desc(aM + (M_2 + 2 * ks) * 128, 128, SBO_M), bt, iKK16, 1u);
+          // dBi[64+s,n] += sum_t M2[t,s] C[t,n]   (A = M2 read MN-major, K = t).  The descriptor
+          // starts eight chunks early so that column s lands in accumulator row 64+s, the lane of
+          // the thread that holds V[s,:]; rows 0-63 of this accumulator are never read.
+          umma_bf16(tmem + TM_DBI, umma_desc_mn(aM + 2 * ks * SBO_M + M_1 * 128 - 8 * 128, SBO_M, 128), ct, iMK16, ks > 0);
+          umma_bf16(tmem + TM_DBI, umma_desc_mn(aM + 2 * ks * SBO_M + M_2 * 128 - 8 * 128, SBO_M, 128), ct, iMK16, 1u);
+        }
+        umma_commit(smem_u32(&bars.d5_full));
+      }
+    }
+  } else {
+    // ===================================================================== main warps
+    const int d = d0 + tid;
+    const bool d_ok = d < p.D;
+    const int cols = min(kDT, p.D - d0);
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t trow = tmem + lane_off;
+    unsigned char* rows = smem + Smem::off_rows;
+    unsigned char* my_row = rows + static_cast<uint32_t>(tid >> 3) * SBO_R + static_cast<uint32_t>(tid & 7) * 16;
+    const float Dv = d_ok ? __ldg(p.Dskip + d) : 0.f;
+    float lam[NS];  // adjoint entering the current chunk from the future
+#pragma unroll
+    for (int n = 0; n < NS; ++n)
+      lam[n] = (p.dhT != nullptr && d_ok && n < p.N) ? p.dhT[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
+    float dDsum = 0.f;
+    uint32_t slab = 0;
+
+    for (int it = 0; it < nchunks; ++it) {
+      const int c = nchunks - 1 - it, t0 = c * Q, len = min(Q, p.T - t0);
+      const uint32_t par = it & 1;
+      const int64_t tile = static_cast<int64_t>(c) * per_chunk + blockIdx.x;
+      // state entering the chunk and state at its end (both saved by the forward)
+      float4 hq[NS / 4], xq[NS / 4];
+      {
+        const float4* xe = reinterpret_cast<const float4*>(p.ckS + (tile * kDT + tid) * NS);
+#pragma unroll
+        for (int q4 = 0; q4 < NS / 4; ++q4) xq[q4] = __ldg(xe + q4);
+        if (c > 0) {
+          const float4* hs = reinterpret_cast<const float4*>(p.ckS + ((tile - per_chunk) * kDT + tid) * NS);
+#pragma unroll
+          for (int q4 = 0; q4 < NS / 4; ++q4) hq[q4] = __ldg(hs + q4);
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < NS / 4; ++q4) {
+            float v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int n = 4 * q4 + k;
+              v[k] = (p.h0 != nullptr && d_ok && n < p.N) ? p.h0[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
+            }
+            hq[q4] = make_float4(v[0], v[1], v[2], v[3]);
+          }
+        }
+      }
+
+      // ---------------- gates: operand rows [al | wt] and the coefficients the epilogue needs
+      float R = 1.f, Rprev = 1.f;
+#pragma unroll 1
+      for (int k = 0; k < NSLAB; ++k, ++slab) {
+        const uint32_t slot = slab % RING, ph = (slab / RING) & 1;
+        if (!mbar_wait(smem_u32(&bars.full[slot]), ph)) timeout();
+        const unsigned char* sl = smem + Smem::off_ring + slot * Smem::slab_bytes;
+        const TA* s_u = reinterpret_cast<const TA*>(sl);
+        const TA* s_fl = s_u + SLAB * kDT;
+        const TA* s_il = s_fl + SLAB * kDT;
+        const TA* s_dy = s_il + SLAB * kDT;
+#pragma unroll
+        for (int j8 = 0; j8 < SLAB / 8; ++j8) {
+          float wv[8], av[8];
+          uint32_t cf[8], ci[8], cu[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int tl = 8 * j8 + j;
+            const float flv = ld_as_f32(s_fl, tl * kDT + tid);
+            const float ilv = fmaxf(ld_as_f32(s_il, tl * kDT + tid), -30.f);
+            const float uv = ld_as_f32(s_u, tl * kDT + tid);
+            const float dyv = ld_as_f32(s_dy, tl * kDT + tid);
+            float a = fast_ex2(flv * kNegLog2e);
+            const float bq = fast_ex2(ilv * kNegLog2e);
+            if (k * SLAB + tl >= len) a = 0.f;       // ragged last chunk: neutral step (f = 1)
+            const float opb = 1.f + bq;
+            R *= 1.f + a;
+            const float r = fast_rcp(R * opb);
+            const float P = opb * r;                 // 1/R
+            const float iR = R * r * R;              // i_t R_t
+            wv[j] = uv * iR;
+            av[j] = dyv * P;
+            cf[j] = __float_as_uint(a * Rprev * P);  // 1 - f_t
+            ci[j] = __float_as_uint(bq * (R * r));   // 1 - i_t
+            cu[j] = __float_as_uint(iR);
+            dDsum = fmaf(dyv, uv, dDsum);
+            Rprev = R;
+          }
+          uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
+          const int ch = k * (SLAB / 8) + j8;
+          split_bf16x2(av[0], av[1], h0, l0); split_bf16x2(av[2], av[3], h1, l1);
+          split_bf16x2(av[4], av[5], h2, l2); split_bf16x2(av[6], av[7], h3, l3);
+          *reinterpret_cast<uint4*>(my_row + (R_A1 + ch) * 128) = make_uint4(h0, h1, h2, h3);
+          *reinterpret_cast<uint4*>(my_row + (R_A2 + ch) * 128) = make_uint4(l0, l1, l2, l3);
+          split_bf16x2(wv[0], wv[1], h0, l0); split_bf16x2(wv[2], wv[3], h1, l1);
+          split_bf16x2(wv[4], wv[5], h2, l2); split_bf16x2(wv[6], wv[7], h3, l3);
+          *reinterpret_cast<uint4*>(my_row + (R_W1 + ch) * 128) = make_uint4(h0, h1, h2, h3);
+          *reinterpret_cast<uint4*>(my_row + (R_W2 + ch) * 128) = make_uint4(l0, l1, l2, l3);
+#define NAJU_TST8(COL, V)                                                                                   \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(trow + (COL) + 8 * ch), \
+               "r"(V[0]), "r"(V[1]), "r"(V[2]), "r"(V[3]), "r"(V[4]), "r"(V[5]), "r"(V[6]), "r"(V[7])          \
+               : "memory")
+          NAJU_TST8(TM_CF, cf);
+          NAJU_TST8(TM_CI, ci);
+          NAJU_TST8(TM_CU, cu);
+#undef NAJU_TST8
+        }
+        mbar_arrive(smem_u32(&bars.empty[slot]));
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (!(R < kRMax)) atomicOr(&p.hdr->status, NAJU_ST_DEEP_TILE);  // never expected here
+      const float PQ = fast_rcp(R);
+      {  // carry rows: h and lt = P_Q lam, two bf16 terms each
+        const float hv[NS] = {hq[0].x, hq[0].y, hq[0].z, hq[0].w, hq[1].x, hq[1].y, hq[1].z, hq[1].w,
+                              hq[2].x, hq[2].y, hq[2].z, hq[2].w, hq[3].x, hq[3].y, hq[3].z, hq[3].w};
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) split_bf16x2(hv[2 * k], hv[2 * k + 1], hi[k], lo[k]);
+        *reinterpret_cast<uint4*>(my_row + (R_H1 + 0) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(my_row + (R_H1 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+        *reinterpret_cast<uint4*>(my_row + (R_H2 + 0) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4*>(my_row + (R_H2 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) split_bf16x2(PQ * lam[2 * k], PQ * lam[2 * k + 1], hi[k], lo[k]);
+        *reinterpret_cast<uint4*>(my_row + (R_L1 + 0) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(my_row + (R_L1 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+        *reinterpret_cast<uint4*>(my_row + (R_L2 + 0) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        *reinterpret_cast<uint4*>(my_row + (R_L2 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars.rows_full));
+
+      // ---------------- epilogue
+      if (!mbar_wait(smem_u32(&bars.d_full), par)) timeout();
+      tc_fence_after();
+      // cross-channel block first, so that the second MMA round overlaps the reverse sweep:
+      // threads t < 64 hold row t of [M2 | U | .], threads 64+s hold row s of [. | . | V]
+      float UV[NS];
+      {
+        uint32_t x[16];
+        if (tid < 64) {
+#pragma unroll
+          for (int s16 = 0; s16 < 4; ++s16) {
+            tmem_ld16_async(trow + TM_X + 16 * s16, x);
+            tmem_ld_wait16(x);
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int s = 16 * s16 + 2 * k;
+              split_bf16x2(s <= tid ? __uint_as_float(x[2 * k]) : 0.f, s + 1 <= tid ? __uint_as_float(x[2 * k + 1]) : 0.f,
+                           hi[k], lo[k]);
+            }
+            unsigned char* mrow = smem + Smem::off_M + static_cast<uint32_t>(tid >> 3) * SBO_M + static_cast<uint32_t>(tid & 7) * 16;
+            *reinterpret_cast<uint4*>(mrow + (M_1 + 2 * s16) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(mrow + (M_1 + 2 * s16 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+            *reinterpret_cast<uint4*>(mrow + (M_2 + 2 * s16) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4*>(mrow + (M_2 + 2 * s16 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+          }
+          tmem_ld16_async(trow + TM_X + 64, x);  // U[t, :]
+        } else {
+          tmem_ld16_async(trow + TM_X + 80, x);  // V[s, :]
+        }
+        tmem_ld_wait16(x);
+#pragma unroll
+        for (int n = 0; n < NS; ++n) UV[n] = __uint_as_float(x[n]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars.m2_full));
+
+      // adjoint leaving the chunk, and the seed of the r recurrence
+      float rr = 0.f;
+      {
+        uint32_t dl[16];
+        tmem_ld16_async(trow + TM_DL, dl);
+        tmem_ld_wait16(dl);
+        const float xe[NS] = {xq[0].x, xq[0].y, xq[0].z, xq[0].w, xq[1].x, xq[1].y, xq[1].z, xq[1].w,
+                              xq[2].x, xq[2].y, xq[2].z, xq[2].w, xq[3].x, xq[3].y, xq[3].z, xq[3].w};
+#pragma unroll
+        for (int n = 0; n < NS; ++n) {
+          rr = fmaf(lam[n], xe[n], rr);
+          lam[n] = fmaf(PQ, lam[n], __uint_as_float(dl[n]));
+        }
+      }
+
+      // reverse-time sweep: 8 steps per round, everything it needs comes from TMEM and this
+      // thread's own operand row
+      unsigned char* out_u = smem + Smem::off_out;
+      unsigned char* out_f = out_u + Q * kDT * 2;
+      unsigned char* out_i = out_f + Q * kDT * 2;
+      const TA* gdy = reinterpret_cast<const TA*>(p.dy) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d;
+#pragma unroll 1
+      for (int ch = Q / 8 - 1; ch >= 0; --ch) {
+        uint32_t y8[8], g8[8], f8[8], i8[8], u8[8];
+#define NAJU_TLD8(COL, V)                                                                                    \
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"                       \
+               : "=r"(V[0]), "=r"(V[1]), "=r"(V[2]), "=r"(V[3]), "=r"(V[4]), "=r"(V[5]), "=r"(V[6]), "=r"(V[7]) \
+               : "r"(trow + (COL) + 8 * ch)                                                                   \
+               : "memory")
+        NAJU_TLD8(TM_Y, y8);
+        NAJU_TLD8(TM_G, g8);
+        NAJU_TLD8(TM_CF, f8);
+        NAJU_TLD8(TM_CI, i8);
+        NAJU_TLD8(TM_CU, u8);
+#undef NAJU_TLD8
+        const uint4 a1 = *reinterpret_cast<const uint4*>(my_row + (R_A1 + ch) * 128);
+        const uint4 a2 = *reinterpret_cast<const uint4*>(my_row + (R_A2 + ch) * 128);
+        const uint4 w1 = *reinterpret_cast<const uint4*>(my_row + (R_W1 + ch) * 128);
+        const uint4 w2 = *reinterpret_cast<const uint4*>(my_row + (R_W2 + ch) * 128);
+        asm volatile("tcgen05.wait::ld.sync.aligned;"
+                     : "+r"(y8[0]), "+r"(y8[1]), "+r"(y8[2]), "+r"(y8[3]), "+r"(y8[4]), "+r"(y8[5]), "+r"(y8[6]), "+r"(y8[7]),
+                       "+r"(g8[0]), "+r"(g8[1]), "+r"(g8[2]), "+r"(g8[3]), "+r"(g8[4]), "+r"(g8[5]), "+r"(g8[6]), "+r"(g8[7])
+                     :
+                     : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;"
+                     : "+r"(f8[0]), "+r"(f8[1]), "+r"(f8[2]), "+r"(f8[3]), "+r"(f8[4]), "+r"(f8[5]), "+r"(f8[6]), "+r"(f8[7]),
+                       "+r"(i8[0]), "+r"(i8[1]), "+r"(i8[2]), "+r"(i8[3]), "+r"(i8[4]), "+r"(i8[5]), "+r"(i8[6]), "+r"(i8[7])
+                     :
+                     : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;"
+                     : "+r"(u8[0]), "+r"(u8[1]), "+r"(u8[2]), "+r"(u8[3]), "+r"(u8[4]), "+r"(u8[5]), "+r"(u8[6]), "+r"(u8[7])
+                     :
+                     : "memory");
+        const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w}, a2w[4] = {a2.x, a2.y, a2.z, a2.w};
+        const uint32_t w1w[4] = {w1.x, w1.y, w1.z, w1.w}, w2w[4] = {w2.x, w2.y, w2.z, w2.w};
+#pragma unroll
+        for (int j = 7; j >= 0; --j) {
+          const int t = 8 * ch + j;
+          const uint32_t pa1 = a1w[j >> 1], pa2 = a2w[j >> 1], pw1 = w1w[j >> 1], pw2 = w2w[j >> 1];
+          const float al = (j & 1) ? bf16hi_f32(pa1) + bf16hi_f32(pa2) : bf16lo_f32(pa1) + bf16lo_f32(pa2);
+          const float wt = (j & 1) ? bf16hi_f32(pw1) + bf16hi_f32(pw2) : bf16lo_f32(pw1) + bf16lo_f32(pw2);
+          const float yt = __uint_as_float(y8[j]), gt = __uint_as_float(g8[j]);
+          rr += fmaf(al, yt, -wt * gt);
+          const float dfl = __uint_as_float(f8[j]) * rr;
+          float du = __uint_as_float(u8[j]) * gt;
+          if (Dv != 0.f && t < len) du = fmaf(Dv, to_f32(gdy[static_cast<int64_t>(t) * p.D]), du);
+          const float dil = wt * __uint_as_float(i8[j]) * gt;
+          reinterpret_cast<TA*>(out_u)[t * kDT + tid] = from_f32<TA>(du);
+          reinterpret_cast<TA*>(out_f)[t * kDT + tid] = from_f32<TA>(dfl);
+          reinterpret_cast<TA*>(out_i)[t * kDT + tid] = from_f32<TA>(dil);
+        }
+      }
+      tc_fence_before();
+      bar_sync<1, NMAIN>();
+      {  // du, d f_logit, d i_logit tiles out with 16-byte stores
+        const int64_t goff = (static_cast<int64_t>(b) * p.T + t0) * p.D + d0;
+        TA* gout[3] = {reinterpret_cast<TA*>(p.du) + goff, reinterpret_cast<TA*>(p.dfl) + goff,
+                       reinterpret_cast<TA*>(p.dil) + goff};
+#pragma unroll
+        for (int w3 = 0; w3 < 3; ++w3) {
+          const unsigned char* src = out_u + w3 * (Q * kDT * 2);
+#pragma unroll
+          for (int i = 0; i < (Q * kDT * 2 / 16) / NMAIN; ++i) {
+            const int v16 = i * NMAIN + tid, t = v16 >> 4, c16 = v16 & 15;
+            if (t < len && c16 * 8 < cols)
+              *reinterpret_cast<uint4*>(gout[w3] + static_cast<int64_t>(t) * p.D + c16 * 8) =
+                  *reinterpret_cast<const uint4*>(src + (t * kDT + c16 * 8) * 2);
+          }
+        }
+      }
+      // dC / dB partial rows of this channel tile: carry part (U, V) + intra-chunk part
+      if (!mbar_wait(smem_u32(&bars.d5_full), par)) timeout();
+      tc_fence_after();
+      {
+        uint32_t x[16];
+        tmem_ld16_async(trow + (tid < 64 ? TM_DCI : TM_DBI), x);
+        tmem_ld_wait16(x);
+        const int tt = tid & 63;
+        if (tt < len) {
+          float* dst = (tid < 64 ? p.dCpart : p.dBpart) +
+                       ((static_cast<int64_t>(b) * p.T + t0 + tt) * p.ndt + dt) * NS;
+#pragma unroll
+          for (int q4 = 0; q4 < NS / 4; ++q4)
+            reinterpret_cast<float4*>(dst)[q4] =
+                make_float4(UV[4 * q4] + __uint_as_float(x[4 * q4]), UV[4 * q4 + 1] + __uint_as_float(x[4 * q4 + 1]),
+                            UV[4 * q4 + 2] + __uint_as_float(x[4 * q4 + 2]), UV[4 * q4 + 3] + __uint_as_float(x[4 * q4 + 3]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars.tile_done));
+      bar_sync<1, NMAIN>();  // rows, output staging and TMEM are free for the next tile
+    }
+    // tile (b, dt) is done: per-row D_skip partial and the gradient of the initial state
+    p.dDpart[static_cast<int64_t>(b) * (p.ndt * kDT) + d0 + tid] = dDsum;
+    if (p.dh0 != nullptr && d_ok) {
+      float* o = p.dh0 + (static_cast<int64_t>(b) * p.D + d) * p.N;
+#pragma unroll
+      for (int n = 0; n < NS; ++n)
+        if (n < p.N) o[n] = lam[n];
+    }
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace tcb
+
+// ------------------------------------------------------------------------------ host side
+namespace {
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn_b() {
+  static EncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+bool make_map_b(CUtensorMap* m, const void* base, int dt, int64_t B, int64_t T, int64_t inner, int64_t sb,
+                int64_t st, int box_inner, int box_t) {
+  const int es = 2;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+  if ((st * es) % 16 != 0 || (sb * es) % 16 != 0 || (box_inner * es) % 16 != 0) return false;
+  if (B > 1 && sb < st) return false;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(st * es), static_cast<cuuint64_t>((B > 1 ? sb : st * T) * es)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_t), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  EncodeFn fn = encode_fn_b();
+  if (!fn) return false;
+  return fn(m, dt == NAJU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count_b() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+
+// Launches the tensor-core backward for this problem if it can take it; returns -1000 if not.
+// The kernel itself stands down unless *fwd_form says the forward ran chunked without deep tiles.
+int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int bc, const int* fwd_form,
+                  void* stream) {
+  if (!(g.N == tcb::NS && g.TC == tcb::Q && act == NAJU_BF16 && gate == NAJU_BF16 && bc == NAJU_BF16)) return -1000;
+  const int64_t ctiles = static_cast<int64_t>(g.B) * g.ndt;
+  if (!(ctiles * 2 >= sm_count_b() && ctiles <= sm_count_b() && g.nchunks >= 4)) return -1000;
+  tcb::Maps maps;
+  const bool ok =
+      make_map_b(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB) &&
+      make_map_b(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tcb::SLAB) &&
+      make_map_b(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tcb::SLAB) &&
+      make_map_b(&maps.dy, p.dy, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::SLAB) &&
+      make_map_b(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tcb::NS, tcb::Q) &&
+      make_map_b(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q);
+  if (!ok) return -1000;
+  auto kern = tcb::bwd_tc_kernel<__nv_bfloat16>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(tcb::Smem::total));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kern<<<static_cast<unsigned>(ctiles), tcb::NTHREADS, tcb::Smem::total, static_cast<cudaStream_t>(stream)>>>(
+      p, maps, fwd_form);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace naju

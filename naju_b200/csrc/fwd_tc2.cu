@@ -231,6 +231,9 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
   tc_fence_after();
   const uint32_t tmem = s_tmem;
   auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
+  if constexpr (WALK) {
+    if (blockIdx.x == 0 && tid == 0) atomicOr(p.fwd_form, 1);  // tell the backward how the forward ran
+  }
 
   if (warp == 8) {
     // ===================================================================== TMA producer
@@ -542,6 +545,7 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
       decode_tile<Q>(static_cast<unsigned>(tile), p.B, p.T, p.D, p.nchunks, p.ndt, tid, tcd);
       const int len = tcd.len;
       if (s_stage_deep[st]) {
+        if (tid == 0) atomicOr(p.fwd_form, 2);
         exact_tile_from_global<TA, TG, WALK>(p, tcd, tid, hc, Pc);
         if constexpr (WALK) {
           if (it + 1 < p.nchunks) write_h_row(hc);

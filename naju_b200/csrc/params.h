@@ -34,14 +34,22 @@ inline Geometry make_geometry(const naju_scan_desc& d) {
 // Checkpoint buffer (persists from forward to backward):
 //   stateS [ntiles][128][NS] fp32  state at the END of each chunk (tile = (chunk, b, dtile))
 //   stateP [ntiles][128]     fp32  product of the retention gate from t=0 to the chunk end
+// Trailer of the checkpoint buffer: how the forward ran, for the backward's kernel choice.
+//   bit 0  the forward ran in the tensor-core chunked form, walking each channel tile in time
+//   bit 1  it met at least one deep-gate tile (the factorised backward cannot take those)
+struct CkptTrailer {
+  int fwd_form;
+};
+
 struct CkptLayout {
-  size_t off_S, off_P, bytes;
+  size_t off_S, off_P, off_trailer, bytes;
 };
 inline CkptLayout ckpt_layout(const Geometry& g) {
   CkptLayout l;
   l.off_S = 0;
   l.off_P = align_up(static_cast<size_t>(g.ntiles) * 128 * g.NS * 4, 256);
-  l.bytes = l.off_P + align_up(static_cast<size_t>(g.ntiles) * 128 * 4, 256);
+  l.off_trailer = l.off_P + align_up(static_cast<size_t>(g.ntiles) * 128 * 4, 256);
+  l.bytes = l.off_trailer + 256;
   return l;
 }
 
@@ -98,6 +106,7 @@ struct FwdParams {
   float* pT;
   float* ckS;
   float* ckP;
+  int* fwd_form;  // CkptTrailer::fwd_form
   ScratchHeader* hdr;
   int* flags;
   float* aggP;
@@ -112,6 +121,8 @@ struct BwdParams {
   const float* h0;
   const float* dhT;
   const float* ckS;
+  const int* fwd_form;  // CkptTrailer::fwd_form; when (fwd_form & 3) == 1 the tensor-core backward runs
+  int tc_launched;      // the tensor-core backward was launched for this call (host decision)
   void *du, *dfl, *dil;
   float* dh0;
   ScratchHeader* hdr;
@@ -136,6 +147,9 @@ int launch_fwd_tc2(const FwdParams& p, const Geometry& g, int act_dtype, int gat
                    void* stream);
 int launch_bwd_simt(const BwdParams& p, const Geometry& g, int act_dtype, int gate_dtype,
                     void* dB, void* dC, float* dD, void* stream);
+// tensor-core backward; returns -1000 when the problem cannot take it
+int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype,
+                  const int* fwd_form, void* stream);
 int launch_step(const naju_scan_desc& d, float* state, const void* u, const void* fl,
                 const void* il, const void* Bm, const void* Cm, const float* Dskip, void* y,
                 void* stream);
