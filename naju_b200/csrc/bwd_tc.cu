@@ -79,6 +79,22 @@ __device__ __forceinline__ uint32_t idesc_bf16(int N, uint32_t a_mn, uint32_t b_
   return umma_idesc(128, N, 1) | (a_mn << 15) | (b_mn << 16);
 }
 
+#ifdef NAJU_PROF
+__device__ unsigned long long g_profb[16];
+#define PROFB_MARK(i)                                                      \
+  do {                                                                     \
+    if (tid == 0) {                                                        \
+      const long long now_ = clock64();                                    \
+      atomicAdd(&g_profb[i], static_cast<unsigned long long>(now_ - pt_)); \
+      pt_ = now_;                                                          \
+    }                                                                      \
+  } while (0)
+#define PROFB_INIT long long pt_ = clock64()
+#else
+#define PROFB_MARK(i) do {} while (0)
+#define PROFB_INIT do {} while (0)
+#endif
+
 struct Maps {
   CUtensorMap u, fl, il, dy, bm, cm;
 };
@@ -248,7 +264,15 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       const uint32_t aCT = sbase + Smem::off_CT, aBT = sbase + Smem::off_BT, aM = sbase + Smem::off_M;
       const uint32_t iKK64 = idesc_bf16(64, 0, 0), iKM64 = idesc_bf16(64, 0, 1), iKK16 = idesc_bf16(16, 0, 0);
       const uint32_t iMM96 = idesc_bf16(96, 1, 1), iMK16 = idesc_bf16(16, 1, 0);
-      auto rowK = [&](int chunk) { return umma_desc(aR + chunk * 128, 128, SBO_R); };  // K-major channel rows
+      // Every operand address is fixed, so the descriptors are built once; a descriptor for another
+      // chunk / row group is the base plus (byte offset >> 4) in its address field.
+      const uint64_t dRk = umma_desc(aR, 128, SBO_R), dRm = umma_desc(aR, SBO_R, 128);     // channel rows
+      const uint64_t dGk = umma_desc(aBG, 128, SBO_BG), dGm = umma_desc(aBG, SBO_BG, 128);  // C | g1 | g2
+      const uint64_t dBB = umma_desc(aBB, 128, SBO_BB), dCT = umma_desc(aCT, 128, SBO_T), dBT = umma_desc(aBT, 128, SBO_T);
+      // M2 operand: K-major as is; MN-major starting eight chunks early, so that column s lands in
+      // accumulator row 64+s (the lane of the thread that holds V[s,:]); rows 0-63 are never read
+      const uint64_t dMk = umma_desc(aM, 128, SBO_M), dMm = umma_desc(aM - 8 * 128, SBO_M, 128);
+      auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
       for (int it = 0; it < nchunks; ++it) {
         const uint32_t par = it & 1;
         if (!mbar_wait(smem_u32(&bars.rows_full), par)) timeout();
@@ -257,38 +281,31 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           // Yt += w1.g1 + w1.g2 + w2.g1   (K = s)
-          const uint64_t g1 = umma_desc(aBG + (BG_G1 + 2 * ks) * 128, 128, SBO_BG);
-          const uint64_t g2 = umma_desc(aBG + (BG_G2 + 2 * ks) * 128, 128, SBO_BG);
-          umma_bf16(tmem + TM_Y, rowK(R_W1 + 2 * ks), g1, iKK64, ks > 0);
-          umma_bf16(tmem + TM_Y, rowK(R_W1 + 2 * ks), g2, iKK64, 1u);
-          umma_bf16(tmem + TM_Y, rowK(R_W2 + 2 * ks), g1, iKK64, 1u);
+          const uint64_t g1 = dGk + off((BG_G1 + 2 * ks) * 128), g2 = dGk + off((BG_G2 + 2 * ks) * 128);
+          umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g1, iKK64, ks > 0);
+          umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g2, iKK64, 1u);
+          umma_bf16(tmem + TM_Y, dRk + off((R_W2 + 2 * ks) * 128), g1, iKK64, 1u);
           // gt += al1.g1^T + al1.g2^T + al2.g1^T   (K = t: the G buffer read MN-major)
-          const uint64_t g1t = umma_desc_mn(aBG + 2 * ks * SBO_BG + BG_G1 * 128, SBO_BG, 128);
-          const uint64_t g2t = umma_desc_mn(aBG + 2 * ks * SBO_BG + BG_G2 * 128, SBO_BG, 128);
-          umma_bf16(tmem + TM_G, rowK(R_A1 + 2 * ks), g1t, iKM64, ks > 0);
-          umma_bf16(tmem + TM_G, rowK(R_A1 + 2 * ks), g2t, iKM64, 1u);
-          umma_bf16(tmem + TM_G, rowK(R_A2 + 2 * ks), g1t, iKM64, 1u);
+          const uint64_t g1t = dGm + off(2 * ks * SBO_BG + BG_G1 * 128), g2t = dGm + off(2 * ks * SBO_BG + BG_G2 * 128);
+          umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g1t, iKM64, ks > 0);
+          umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g2t, iKM64, 1u);
+          umma_bf16(tmem + TM_G, dRk + off((R_A2 + 2 * ks) * 128), g1t, iKM64, 1u);
           // dL += al1.C + al2.C   (K = t, B operand = C^T rows)
-          const uint64_t ct = umma_desc(aCT + 2 * ks * 128, 128, SBO_T);
-          umma_bf16(tmem + TM_DL, rowK(R_A1 + 2 * ks), ct, iKK16, ks > 0);
-          umma_bf16(tmem + TM_DL, rowK(R_A2 + 2 * ks), ct, iKK16, 1u);
+          umma_bf16(tmem + TM_DL, dRk + off((R_A1 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, ks > 0);
+          umma_bf16(tmem + TM_DL, dRk + off((R_A2 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, 1u);
         }
-        {  // Yt += (h1 + h2).C,  gt += (l1 + l2).B   (K = n)
-          const uint64_t cc = umma_desc(aBG + BG_C * 128, 128, SBO_BG), bb = umma_desc(aBB, 128, SBO_BB);
-          umma_bf16(tmem + TM_Y, rowK(R_H1), cc, iKK64, 1u);
-          umma_bf16(tmem + TM_Y, rowK(R_H2), cc, iKK64, 1u);
-          umma_bf16(tmem + TM_G, rowK(R_L1), bb, iKK64, 1u);
-          umma_bf16(tmem + TM_G, rowK(R_L2), bb, iKK64, 1u);
-        }
+        // Yt += (h1 + h2).C,  gt += (l1 + l2).B   (K = n)
+        umma_bf16(tmem + TM_Y, dRk + off(R_H1 * 128), dGk + off(BG_C * 128), iKK64, 1u);
+        umma_bf16(tmem + TM_Y, dRk + off(R_H2 * 128), dGk + off(BG_C * 128), iKK64, 1u);
+        umma_bf16(tmem + TM_G, dRk + off(R_L1 * 128), dBB, iKK64, 1u);
+        umma_bf16(tmem + TM_G, dRk + off(R_L2 * 128), dBB, iKK64, 1u);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           // cross-channel: X[m, n'] += [al | wt]^T . [wt | h | lt]   (K = 16 channels per step)
-          const uint32_t grp = aR + 2 * ks * SBO_R;
-          const uint64_t A1 = umma_desc_mn(grp + R_A1 * 128, SBO_R, 128), A2 = umma_desc_mn(grp + R_A2 * 128, SBO_R, 128);
-          const uint64_t B1 = umma_desc_mn(grp + R_W1 * 128, SBO_R, 128), B2 = umma_desc_mn(grp + R_W2 * 128, SBO_R, 128);
-          umma_bf16(tmem + TM_X, A1, B1, iMM96, ks > 0);
-          umma_bf16(tmem + TM_X, A1, B2, iMM96, 1u);
-          umma_bf16(tmem + TM_X, A2, B1, iMM96, 1u);
+          const uint64_t grp = dRm + off(2 * ks * SBO_R);
+          umma_bf16(tmem + TM_X, grp + off(R_A1 * 128), grp + off(R_W1 * 128), iMM96, ks > 0);
+          umma_bf16(tmem + TM_X, grp + off(R_A1 * 128), grp + off(R_W2 * 128), iMM96, 1u);
+          umma_bf16(tmem + TM_X, grp + off(R_A2 * 128), grp + off(R_W1 * 128), iMM96, 1u);
         }
         umma_commit(smem_u32(&bars.d_full));
         // second round: the intra-chunk parts of dC and dB from the masked M2 the main warps wrote
@@ -296,15 +313,12 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t bt = umma_desc(aBT + 2 * ks * 128, 128, SBO_T), ct = umma_desc(aCT + 2 * ks * 128, 128, SBO_T);
           // dCi[t,n] += sum_s M2[t,s] B[s,n]    (A = M2 rows, K = s)
-          umma_bf16(tmem + TM_DCI, umma_desc(aM + (M_1 + 2 * ks) * 128, 128, SBO_M), bt, iKK16, ks > 0);
-          umma_bf16(tmem + TM_DCI, umma_desc(aM + (M_2 + 2 * ks) * 128, 128, SBO_M), bt, iKK16, 1u);
-          // dBi[64+s,n] += sum_t M2[t,s] C[t,n]   (A = M2 read MN-major, K = t).  The descriptor
-          // starts eight chunks early so that column s lands in accumulator row 64+s, the lane of
-          // the thread that holds V[s,:]; rows 0-63 of this accumulator are never read.
-          umma_bf16(tmem + TM_DBI, umma_desc_mn(aM + 2 * ks * SBO_M + M_1 * 128 - 8 * 128, SBO_M, 128), ct, iMK16, ks > 0);
-          umma_bf16(tmem + TM_DBI, umma_desc_mn(aM + 2 * ks * SBO_M + M_2 * 128 - 8 * 128, SBO_M, 128), ct, iMK16, 1u);
+          umma_bf16(tmem + TM_DCI, dMk + off((M_1 + 2 * ks) * 128), dBT + off(2 * ks * 128), iKK16, ks > 0);
+          umma_bf16(tmem + TM_DCI, dMk + off((M_2 + 2 * ks) * 128), dBT + off(2 * ks * 128), iKK16, 1u);
+          // dBi[64+s,n] += sum_t M2[t,s] C[t,n]   (A = M2 read MN-major, K = t)
+          umma_bf16(tmem + TM_DBI, dMm + off(2 * ks * SBO_M + M_1 * 128), dCT + off(2 * ks * 128), iMK16, ks > 0);
+          umma_bf16(tmem + TM_DBI, dMm + off(2 * ks * SBO_M + M_2 * 128), dCT + off(2 * ks * 128), iMK16, 1u);
         }
         umma_commit(smem_u32(&bars.d5_full));
       }
@@ -325,6 +339,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       lam[n] = (p.dhT != nullptr && d_ok && n < p.N) ? p.dhT[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
     float dDsum = 0.f;
     uint32_t slab = 0;
+    PROFB_INIT;
 
     for (int it = 0; it < nchunks; ++it) {
       const int c = nchunks - 1 - it, t0 = c * Q, len = min(Q, p.T - t0);
@@ -354,6 +369,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
       }
 
+      PROFB_MARK(0);
       // ---------------- gates: operand rows [al | wt] and the coefficients the epilogue needs
       float R = 1.f, Rprev = 1.f;
 #pragma unroll 1
@@ -414,6 +430,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         mbar_arrive(smem_u32(&bars.empty[slot]));
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      PROFB_MARK(1);
       if (!(R < kRMax)) atomicOr(&p.hdr->status, NAJU_ST_DEEP_TILE);  // never expected here
       const float PQ = fast_rcp(R);
       {  // carry rows: h and lt = P_Q lam, two bf16 terms each
@@ -437,9 +454,11 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       tc_fence_before();
       mbar_arrive(smem_u32(&bars.rows_full));
 
+      PROFB_MARK(2);
       // ---------------- epilogue
       if (!mbar_wait(smem_u32(&bars.d_full), par)) timeout();
       tc_fence_after();
+      PROFB_MARK(3);
       // cross-channel block first, so that the second MMA round overlaps the reverse sweep:
       // threads t < 64 hold row t of [M2 | U | .], threads 64+s hold row s of [. | . | V]
       float UV[NS];
@@ -475,6 +494,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       tc_fence_before();
       mbar_arrive(smem_u32(&bars.m2_full));
 
+      PROFB_MARK(4);
       // adjoint leaving the chunk, and the seed of the r recurrence
       float rr = 0.f;
       {
@@ -490,44 +510,60 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
       }
 
+      PROFB_MARK(5);
       // reverse-time sweep: 8 steps per round, everything it needs comes from TMEM and this
       // thread's own operand row
       unsigned char* out_u = smem + Smem::off_out;
       unsigned char* out_f = out_u + Q * kDT * 2;
       unsigned char* out_i = out_f + Q * kDT * 2;
       const TA* gdy = reinterpret_cast<const TA*>(p.dy) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d;
-#pragma unroll 1
-      for (int ch = Q / 8 - 1; ch >= 0; --ch) {
-        uint32_t y8[8], g8[8], f8[8], i8[8], u8[8];
-#define NAJU_TLD8(COL, V)                                                                                    \
+      // TMEM loads are software-pipelined: round ch-1 is in flight while round ch is processed
+      uint32_t tq[2][5][8];
+#define NAJU_TLD8(COL, V, CH)                                                                                \
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"                       \
                : "=r"(V[0]), "=r"(V[1]), "=r"(V[2]), "=r"(V[3]), "=r"(V[4]), "=r"(V[5]), "=r"(V[6]), "=r"(V[7]) \
-               : "r"(trow + (COL) + 8 * ch)                                                                   \
+               : "r"(trow + (COL) + 8 * (CH))                                                                 \
                : "memory")
-        NAJU_TLD8(TM_Y, y8);
-        NAJU_TLD8(TM_G, g8);
-        NAJU_TLD8(TM_CF, f8);
-        NAJU_TLD8(TM_CI, i8);
-        NAJU_TLD8(TM_CU, u8);
-#undef NAJU_TLD8
+#define NAJU_TWAIT16(A, B)                                                                                   \
+  asm volatile("tcgen05.wait::ld.sync.aligned;"                                                              \
+               : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "+r"(A[4]), "+r"(A[5]), "+r"(A[6]), "+r"(A[7]), \
+                 "+r"(B[0]), "+r"(B[1]), "+r"(B[2]), "+r"(B[3]), "+r"(B[4]), "+r"(B[5]), "+r"(B[6]), "+r"(B[7])  \
+               :                                                                                             \
+               : "memory")
+#define NAJU_TWAIT8(A)                                                                                       \
+  asm volatile("tcgen05.wait::ld.sync.aligned;"                                                              \
+               : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "+r"(A[4]), "+r"(A[5]), "+r"(A[6]), "+r"(A[7]) \
+               :                                                                                             \
+               : "memory")
+#define NAJU_TLOAD_ROUND(BUF, CH)          \
+  do {                                     \
+    NAJU_TLD8(TM_Y, tq[BUF][0], CH);       \
+    NAJU_TLD8(TM_G, tq[BUF][1], CH);       \
+    NAJU_TLD8(TM_CF, tq[BUF][2], CH);      \
+    NAJU_TLD8(TM_CI, tq[BUF][3], CH);      \
+    NAJU_TLD8(TM_CU, tq[BUF][4], CH);      \
+  } while (0)
+#define NAJU_TWAIT_ROUND(BUF)                  \
+  do {                                         \
+    NAJU_TWAIT16(tq[BUF][0], tq[BUF][1]);      \
+    NAJU_TWAIT16(tq[BUF][2], tq[BUF][3]);      \
+    NAJU_TWAIT8(tq[BUF][4]);                   \
+  } while (0)
+      NAJU_TLOAD_ROUND(1, Q / 8 - 1);
+      NAJU_TWAIT_ROUND(1);
+#pragma unroll
+      for (int ch = Q / 8 - 1; ch >= 0; --ch) {
+        const int cur = ch & 1, nxt = cur ^ 1;
+        if (ch > 0) NAJU_TLOAD_ROUND(nxt, ch - 1);
+        const uint32_t* y8 = tq[cur][0];
+        const uint32_t* g8 = tq[cur][1];
+        const uint32_t* f8 = tq[cur][2];
+        const uint32_t* i8 = tq[cur][3];
+        const uint32_t* u8 = tq[cur][4];
         const uint4 a1 = *reinterpret_cast<const uint4*>(my_row + (R_A1 + ch) * 128);
         const uint4 a2 = *reinterpret_cast<const uint4*>(my_row + (R_A2 + ch) * 128);
         const uint4 w1 = *reinterpret_cast<const uint4*>(my_row + (R_W1 + ch) * 128);
         const uint4 w2 = *reinterpret_cast<const uint4*>(my_row + (R_W2 + ch) * 128);
-        asm volatile("tcgen05.wait::ld.sync.aligned;"
-                     : "+r"(y8[0]), "+r"(y8[1]), "+r"(y8[2]), "+r"(y8[3]), "+r"(y8[4]), "+r"(y8[5]), "+r"(y8[6]), "+r"(y8[7]),
-                       "+r"(g8[0]), "+r"(g8[1]), "+r"(g8[2]), "+r"(g8[3]), "+r"(g8[4]), "+r"(g8[5]), "+r"(g8[6]), "+r"(g8[7])
-                     :
-                     : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;"
-                     : "+r"(f8[0]), "+r"(f8[1]), "+r"(f8[2]), "+r"(f8[3]), "+r"(f8[4]), "+r"(f8[5]), "+r"(f8[6]), "+r"(f8[7]),
-                       "+r"(i8[0]), "+r"(i8[1]), "+r"(i8[2]), "+r"(i8[3]), "+r"(i8[4]), "+r"(i8[5]), "+r"(i8[6]), "+r"(i8[7])
-                     :
-                     : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;"
-                     : "+r"(u8[0]), "+r"(u8[1]), "+r"(u8[2]), "+r"(u8[3]), "+r"(u8[4]), "+r"(u8[5]), "+r"(u8[6]), "+r"(u8[7])
-                     :
-                     : "memory");
         const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w}, a2w[4] = {a2.x, a2.y, a2.z, a2.w};
         const uint32_t w1w[4] = {w1.x, w1.y, w1.z, w1.w}, w2w[4] = {w2.x, w2.y, w2.z, w2.w};
 #pragma unroll
@@ -546,7 +582,14 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           reinterpret_cast<TA*>(out_f)[t * kDT + tid] = from_f32<TA>(dfl);
           reinterpret_cast<TA*>(out_i)[t * kDT + tid] = from_f32<TA>(dil);
         }
+        if (ch > 0) NAJU_TWAIT_ROUND(nxt);
       }
+#undef NAJU_TLD8
+#undef NAJU_TWAIT16
+#undef NAJU_TWAIT8
+#undef NAJU_TLOAD_ROUND
+#undef NAJU_TWAIT_ROUND
+      PROFB_MARK(6);
       tc_fence_before();
       bar_sync<1, NMAIN>();
       {  // du, d f_logit, d i_logit tiles out with 16-byte stores
@@ -565,6 +608,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           }
         }
       }
+      PROFB_MARK(7);
       // dC / dB partial rows of this channel tile: carry part (U, V) + intra-chunk part
       if (!mbar_wait(smem_u32(&bars.d5_full), par)) timeout();
       tc_fence_after();
@@ -586,6 +630,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       tc_fence_before();
       mbar_arrive(smem_u32(&bars.tile_done));
       bar_sync<1, NMAIN>();  // rows, output staging and TMEM are free for the next tile
+      PROFB_MARK(8);
     }
     // tile (b, dt) is done: per-row D_skip partial and the gradient of the initial state
     p.dDpart[static_cast<int64_t>(b) * (p.ndt * kDT) + d0 + tid] = dDsum;
@@ -601,6 +646,18 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 }
 
 }  // namespace tcb
+
+#ifdef NAJU_PROF
+}  // namespace naju
+extern "C" int naju_b200_debug_prof_bwd(unsigned long long* out16, int reset) {
+  if (reset) {
+    unsigned long long z[16] = {};
+    return static_cast<int>(cudaMemcpyToSymbol(naju::tcb::g_profb, z, sizeof(z)));
+  }
+  return static_cast<int>(cudaMemcpyFromSymbol(out16, naju::tcb::g_profb, 16 * sizeof(unsigned long long)));
+}
+namespace naju {
+#endif
 
 // ------------------------------------------------------------------------------ host side
 namespace {

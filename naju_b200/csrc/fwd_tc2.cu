@@ -348,7 +348,10 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
   } else if (warp == 10) {
     // ===================================================================== MMA issuer
     const uint32_t id16 = umma_idesc(128, NS, 1), id64 = umma_idesc(128, Q, 1);
-    const uint32_t aAH = sbase + SM::off_AH;
+    // operand addresses are fixed: build the descriptors once, offset the address field per use
+    const uint64_t dAW0 = umma_desc(sbase + SM::off_AW, 128, SBO_AW), dAH = umma_desc(sbase + SM::off_AH, 128, SBO_AH);
+    const uint64_t dB10 = umma_desc(sbase + SM::off_B1, 128, SBO_B1), dB20 = umma_desc(sbase + SM::off_B2, 128, SBO_B2);
+    auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
     uint32_t hph = 0;  // parity of the next h_ready phase (one per tile)
     for (int it = 0;; ++it) {
       const int st = it & 1;
@@ -368,15 +371,12 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
         } else {
           if (!mbar_wait(smem_u32(&bars.ops_full[st]), par)) timeout();
           tc_fence_after();
-          const uint32_t aAW = sbase + SM::off_AW + st * AW_BYTES;
-          const uint32_t aB1 = sbase + SM::off_B1 + st * B1_BYTES;
-          const uint32_t aB2 = sbase + SM::off_B2 + st * B2_BYTES;
+          const uint64_t dAW = dAW0 + off(st * AW_BYTES), dB1 = dB10 + off(st * B1_BYTES), dB2 = dB20 + off(st * B2_BYTES);
           const uint32_t tst = tmem + st * TM_STAGE;
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {  // D2 = (w1 | w2) . B^T
             const int ach = (ks < 4 ? AW_W1 : AW_W2) + 2 * (ks & 3);
-            umma_bf16(tst + TM_D2, umma_desc(aAW + ach * 128, 128, SBO_AW),
-                      umma_desc(aB2 + 2 * (ks & 3) * 128, 128, SBO_B2), id16, ks > 0);
+            umma_bf16(tst + TM_D2, dAW + off(ach * 128), dB2 + off(2 * (ks & 3) * 128), id16, ks > 0);
           }
           umma_commit(smem_u32(&bars.d2_full[st]));
 #ifdef NAJU_PROF
@@ -390,8 +390,7 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
           for (int ks = 0; ks < 12; ++ks) {  // D1 = w1.g1 + w1.g2 + w2.g1
             const int ach = (ks < 8 ? AW_W1 : AW_W2) + 2 * (ks & 3);
             const int bch = ((ks >= 4 && ks < 8) ? B1_G2 : B1_G1) + 2 * (ks & 3);
-            umma_bf16(tst + TM_D1, umma_desc(aAW + ach * 128, 128, SBO_AW),
-                      umma_desc(aB1 + bch * 128, 128, SBO_B1), id64, ks > 0);
+            umma_bf16(tst + TM_D1, dAW + off(ach * 128), dB1 + off(bch * 128), id64, ks > 0);
           }
 #ifdef NAJU_PROF
           const long long t_b = clock64();
@@ -403,10 +402,8 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
           const long long t_c = clock64();
 #endif
           tc_fence_after();
-          umma_bf16(tst + TM_D1, umma_desc(aAH + AH_H1 * 128, 128, SBO_AH), umma_desc(aB1 + B1_C * 128, 128, SBO_B1),
-                    id64, 1u);
-          umma_bf16(tst + TM_D1, umma_desc(aAH + AH_H2 * 128, 128, SBO_AH), umma_desc(aB1 + B1_C * 128, 128, SBO_B1),
-                    id64, 1u);
+          umma_bf16(tst + TM_D1, dAH + off(AH_H1 * 128), dB1 + off(B1_C * 128), id64, 1u);
+          umma_bf16(tst + TM_D1, dAH + off(AH_H2 * 128), dB1 + off(B1_C * 128), id64, 1u);
           umma_commit(smem_u32(&bars.d1_full));
 #ifdef NAJU_PROF
           mbar_wait(smem_u32(&bars.d1_full), (unsigned)(it & 1));
