@@ -349,7 +349,7 @@ __global__ void finalize_bc_kernel(const float* __restrict__ part, void* __restr
 __global__ void finalize_dD_kernel(const float* __restrict__ part, float* __restrict__ dD,
                                    int rows, int rows_tc, const int* __restrict__ fwd_form, int ld, int D) {
   __shared__ float red[32][33];
-  // the tensor-core backward writes one partial row per batch row, the recurrent one per chunk
+  // the tensor-core backward writes two partial rows per batch row, the recurrent one per chunk
   if (rows_tc > 0 && (*fwd_form & 3) == 1) rows = rows_tc;
   const int dl = threadIdx.x, rl = threadIdx.y;
   const int d = blockIdx.x * 32 + dl;
@@ -408,7 +408,7 @@ int launch_bwd_simt(const BwdParams& p, const Geometry& g, int act, int gate, vo
   finalize_bc_kernel<<<blocks, 256, 0, st>>>(p.dBpart, dB, rows, g.ndt, g.NS, g.N, p.bc_dtype);
   finalize_bc_kernel<<<blocks, 256, 0, st>>>(p.dCpart, dC, rows, g.ndt, g.NS, g.N, p.bc_dtype);
   finalize_dD_kernel<<<(g.D + 31) / 32, dim3(32, 32), 0, st>>>(p.dDpart, dD, g.nchunks * g.B,
-                                                              p.tc_launched ? g.B : 0, p.fwd_form,
+                                                              p.tc_launched ? 2 * g.B : 0, p.fwd_form,
                                                               g.ndt * kDT, g.D);
   return static_cast<int>(cudaGetLastError());
 }

@@ -39,8 +39,8 @@ namespace tcb {
 
 using namespace tcx;
 
-constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, RING = 3;
-constexpr int NMAIN = 128, NTHREADS = 224;
+constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, RING = 4;
+constexpr int NMAIN = 256, NHALF = 128, NTHREADS = 352;
 // channel row (bf16, chunks of 8): [al1 8 | w1 8 | h1 2 | l1 2 | al2 8 | w2 8 | h2 2 | l2 2]
 constexpr int R_A1 = 0, R_W1 = 8, R_H1 = 16, R_L1 = 18, R_A2 = 20, R_W2 = 28, R_H2 = 36, R_L2 = 38, R_CH = 40;
 constexpr uint32_t SBO_R = R_CH * 128, ROWS_BYTES = 16 * SBO_R;  // 81920
@@ -107,16 +107,22 @@ struct Smem {
   static constexpr uint32_t off_BB = off_BG + BG_BYTES;
   static constexpr uint32_t off_CT = off_BB + BB_BYTES;
   static constexpr uint32_t off_BT = off_CT + T_BYTES;
-  static constexpr uint32_t off_M = off_BT + T_BYTES;
-  static constexpr uint32_t off_bc = off_M + M_BYTES;           // [2 tiles][B raw | C raw]
+  static constexpr uint32_t off_bc = off_BT + T_BYTES;            // [2 tiles][B raw | C raw]
   static constexpr uint32_t off_out = off_bc + 2 * 2 * BC_BYTES;  // du | dfl | dil, [64][128] each
+  // The M2 operand re-uses the du staging tile: it is written after the staged outputs have been
+  // stored and consumed (second MMA round) before the next sweep stages anything.
+  static constexpr uint32_t off_M = off_out;
   static constexpr uint32_t total = off_out + 3 * Q * kDT * 2;
 };
 
 struct Bars {
   unsigned long long full[RING], empty[RING];
   unsigned long long bc_full[2], bc_empty[2];
-  unsigned long long rows_full, ops_full, d_full, m2_full, d5_full, tile_done;
+  unsigned long long part[NSLAB];  // operand-row chunks of one 16-step slab written (128 threads)
+  unsigned long long carry_full;   // h and lt rows written
+  unsigned long long opsA_full;    // C | g1 | g2 and B rows built (first MMA round, contraction over time/state)
+  unsigned long long opsB_full;    // C^T and B^T built (dL and the second MMA round)
+  unsigned long long d1_full, d4_full, m2_full, d5_full, tile_done;
 };
 
 template <typename TA>
@@ -126,6 +132,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ Bars bars;
   __shared__ unsigned int s_tmem;
+  __shared__ float s_PQ[kDT];  // chunk retention product per channel (second-half threads -> first-half)
 
   // stand down unless the forward ran in the chunked form and met no deep-gate tile
   if ((*fwd_form & 3) != 1) return;
@@ -146,17 +153,19 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       mbar_init(smem_u32(&bars.bc_full[i]), 1);
       mbar_init(smem_u32(&bars.bc_empty[i]), 1);
     }
-    mbar_init(smem_u32(&bars.rows_full), NMAIN);
-    mbar_init(smem_u32(&bars.ops_full), 1);
-    mbar_init(smem_u32(&bars.d_full), 1);
+    for (int i = 0; i < NSLAB; ++i) mbar_init(smem_u32(&bars.part[i]), NHALF);
+    mbar_init(smem_u32(&bars.carry_full), NMAIN);
+    mbar_init(smem_u32(&bars.opsA_full), 1);
+    mbar_init(smem_u32(&bars.opsB_full), 1);
+    mbar_init(smem_u32(&bars.d1_full), 1);
+    mbar_init(smem_u32(&bars.d4_full), 1);
     mbar_init(smem_u32(&bars.m2_full), NMAIN);
     mbar_init(smem_u32(&bars.d5_full), 1);
     mbar_init(smem_u32(&bars.tile_done), NMAIN);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
-  // zero the operand buffers once: the upper triangle of g1/g2 and of the M2 operand, and the
-  // unused M2 rows, are never written afterwards
+  // zero the shared operand buffers once: the upper triangle of g1/g2 is never written afterwards
   for (uint32_t i = tid * 16; i < Smem::off_bc - Smem::off_BG; i += NTHREADS * 16)
     *reinterpret_cast<uint4*>(smem + Smem::off_BG + i) = make_uint4(0, 0, 0, 0);
   fence_async_smem();
@@ -166,7 +175,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
   const uint32_t tmem = s_tmem;
   auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ===================================================================== TMA producer
     if (lane == 0) {
       uint32_t slab = 0;
@@ -193,7 +202,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ===================================================================== operand builder
     const int g = lane >> 2, t4 = lane & 3;
     unsigned char* s_BG = smem + Smem::off_BG;
@@ -203,8 +212,9 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     for (int it = 0; it < nchunks; ++it) {
       const int par = it & 1;
       if (!mbar_wait(smem_u32(&bars.bc_full[par]), (it >> 1) & 1)) timeout();
-      // the previous tile's MMAs (and its last reads of these buffers) must be over
-      if (it >= 1 && !mbar_wait(smem_u32(&bars.tile_done), (it - 1) & 1)) timeout();
+      // C | g1 | g2 and the B rows are read only by the previous tile's first MMA round: they can
+      // be rebuilt as soon as that round is complete, while the previous tile is still in its sweep
+      if (it >= 1 && !mbar_wait(smem_u32(&bars.d1_full), (it - 1) & 1)) timeout();
       const __nv_bfloat16* Braw = reinterpret_cast<const __nv_bfloat16*>(smem + Smem::off_bc + par * 2 * BC_BYTES);
       const __nv_bfloat16* Craw = Braw + Q * NS;
       for (int e = lane; e < Q * 2; e += 32) {  // C into BG, B into BB: rows of 32 bytes
@@ -213,20 +223,6 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
             *reinterpret_cast<const uint4*>(Craw + t * NS + half * 8);
         *reinterpret_cast<uint4*>(s_BB + op_off16(t, half * 8, SBO_BB)) =
             *reinterpret_cast<const uint4*>(Braw + t * NS + half * 8);
-      }
-      for (int e = lane; e < NS * (Q / 8); e += 32) {  // C^T and B^T: (row n, eight columns t)
-        const int n = e % NS, s8 = e / NS;
-        uint32_t wc[4], wb[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r0 = (8 * s8 + 2 * j) * NS + n, r1 = r0 + NS;
-          wc[j] = static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Craw)[r0]) |
-                  (static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Craw)[r1]) << 16);
-          wb[j] = static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Braw)[r0]) |
-                  (static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Braw)[r1]) << 16);
-        }
-        *reinterpret_cast<uint4*>(s_CT + op_off16(n, 8 * s8, SBO_T)) = make_uint4(wc[0], wc[1], wc[2], wc[3]);
-        *reinterpret_cast<uint4*>(s_BT + op_off16(n, 8 * s8, SBO_T)) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
       }
 #pragma unroll 1
       for (int mt = 0; mt < Q / 16; ++mt) {  // G = tril(C B^T), two bf16 terms
@@ -252,12 +248,31 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       }
       fence_async_smem();
       __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars.opsA_full));
+      // C^T and B^T are still read by the previous tile's second MMA round
+      if (it >= 1 && !mbar_wait(smem_u32(&bars.d5_full), (it - 1) & 1)) timeout();
+      for (int e = lane; e < NS * (Q / 8); e += 32) {  // C^T and B^T: (row n, eight columns t)
+        const int n = e % NS, s8 = e / NS;
+        uint32_t wc[4], wb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r0 = (8 * s8 + 2 * j) * NS + n, r1 = r0 + NS;
+          wc[j] = static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Craw)[r0]) |
+                  (static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Craw)[r1]) << 16);
+          wb[j] = static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Braw)[r0]) |
+                  (static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(Braw)[r1]) << 16);
+        }
+        *reinterpret_cast<uint4*>(s_CT + op_off16(n, 8 * s8, SBO_T)) = make_uint4(wc[0], wc[1], wc[2], wc[3]);
+        *reinterpret_cast<uint4*>(s_BT + op_off16(n, 8 * s8, SBO_T)) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+      }
+      fence_async_smem();
+      __syncwarp();
       if (lane == 0) {
-        mbar_arrive(smem_u32(&bars.ops_full));
+        mbar_arrive(smem_u32(&bars.opsB_full));
         mbar_arrive(smem_u32(&bars.bc_empty[par]));
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     // ===================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t aR = sbase + Smem::off_rows, aBG = sbase + Smem::off_BG, aBB = sbase + Smem::off_BB;
@@ -275,11 +290,19 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
       for (int it = 0; it < nchunks; ++it) {
         const uint32_t par = it & 1;
-        if (!mbar_wait(smem_u32(&bars.rows_full), par)) timeout();
-        if (!mbar_wait(smem_u32(&bars.ops_full), par)) timeout();
-        tc_fence_after();
+        if (!mbar_wait(smem_u32(&bars.opsA_full), par)) timeout();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
+          // the MMAs that contract over time need only the row chunks of slab ks: they run while
+          // the main warps are still evaluating the gates of the other slabs
+#ifdef NAJU_PROF
+          const long long t_p = clock64();
+#endif
+          if (!mbar_wait(smem_u32(&bars.part[ks]), par)) timeout();
+#ifdef NAJU_PROF
+          atomicAdd(&g_profb[12 + (ks >> 1)], static_cast<unsigned long long>(clock64() - t_p));
+#endif
+          tc_fence_after();
           // Yt += w1.g1 + w1.g2 + w2.g1   (K = s)
           const uint64_t g1 = dGk + off((BG_G1 + 2 * ks) * 128), g2 = dGk + off((BG_G2 + 2 * ks) * 128);
           umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g1, iKK64, ks > 0);
@@ -290,24 +313,45 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g1t, iKM64, ks > 0);
           umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g2t, iKM64, 1u);
           umma_bf16(tmem + TM_G, dRk + off((R_A2 + 2 * ks) * 128), g1t, iKM64, 1u);
-          // dL += al1.C + al2.C   (K = t, B operand = C^T rows)
+        }
+        // dL += al1.C + al2.C   (K = t, B operand = C^T rows)
+        if (!mbar_wait(smem_u32(&bars.opsB_full), par)) timeout();
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
           umma_bf16(tmem + TM_DL, dRk + off((R_A1 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, ks > 0);
           umma_bf16(tmem + TM_DL, dRk + off((R_A2 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, 1u);
         }
         // Yt += (h1 + h2).C,  gt += (l1 + l2).B   (K = n)
+        if (!mbar_wait(smem_u32(&bars.carry_full), par)) timeout();
+        tc_fence_after();
         umma_bf16(tmem + TM_Y, dRk + off(R_H1 * 128), dGk + off(BG_C * 128), iKK64, 1u);
         umma_bf16(tmem + TM_Y, dRk + off(R_H2 * 128), dGk + off(BG_C * 128), iKK64, 1u);
         umma_bf16(tmem + TM_G, dRk + off(R_L1 * 128), dBB, iKK64, 1u);
         umma_bf16(tmem + TM_G, dRk + off(R_L2 * 128), dBB, iKK64, 1u);
+        umma_commit(smem_u32(&bars.d1_full));  // the reverse sweep can start
+#ifdef NAJU_PROF
+        {
+          const long long t_a = clock64();
+          mbar_wait(smem_u32(&bars.d1_full), par);
+          atomicAdd(&g_profb[10], static_cast<unsigned long long>(clock64() - t_a));
+        }
+        const long long t_x = clock64();
+#endif
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          // cross-channel: X[m, n'] += [al | wt]^T . [wt | h | lt]   (K = 16 channels per step)
+          // cross-channel: X[m, n'] += [al | wt]^T . [wt | h | lt]   (K = 16 channels per step);
+          // these run on the tensor cores while the main warps do the sweep
           const uint64_t grp = dRm + off(2 * ks * SBO_R);
           umma_bf16(tmem + TM_X, grp + off(R_A1 * 128), grp + off(R_W1 * 128), iMM96, ks > 0);
           umma_bf16(tmem + TM_X, grp + off(R_A1 * 128), grp + off(R_W2 * 128), iMM96, 1u);
           umma_bf16(tmem + TM_X, grp + off(R_A2 * 128), grp + off(R_W1 * 128), iMM96, 1u);
         }
-        umma_commit(smem_u32(&bars.d_full));
+        umma_commit(smem_u32(&bars.d4_full));
+#ifdef NAJU_PROF
+        mbar_wait(smem_u32(&bars.d4_full), par);
+        atomicAdd(&g_profb[11], static_cast<unsigned long long>(clock64() - t_x));
+#endif
         // second round: the intra-chunk parts of dC and dB from the masked M2 the main warps wrote
         if (!mbar_wait(smem_u32(&bars.m2_full), par)) timeout();
         tc_fence_after();
@@ -325,62 +369,131 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     }
   } else {
     // ===================================================================== main warps
-    const int d = d0 + tid;
+    // Two threads per channel: warps 0-3 ("first half") own steps 0-31 of every chunk, warps 4-7
+    // ("second half") steps 32-63; warps w and w+4 sit on the same TMEM lane quarter.  Neither half
+    // waits for the other: the second half first runs a cheap product-only pass over steps 0-31 to
+    // get R_32, and in the reverse sweep the first half first sums the r-increments of steps
+    // 63-32 to get r_32.
+    const int half = warp >> 2;
+    const int cid = tid & (kDT - 1);  // channel within the tile
+    const int d = d0 + cid;
     const bool d_ok = d < p.D;
     const int cols = min(kDT, p.D - d0);
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t trow = tmem + lane_off;
+    const uint32_t trow = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     unsigned char* rows = smem + Smem::off_rows;
-    unsigned char* my_row = rows + static_cast<uint32_t>(tid >> 3) * SBO_R + static_cast<uint32_t>(tid & 7) * 16;
+    unsigned char* my_row = rows + static_cast<uint32_t>(cid >> 3) * SBO_R + static_cast<uint32_t>(cid & 7) * 16;
     const float Dv = d_ok ? __ldg(p.Dskip + d) : 0.f;
-    float lam[NS];  // adjoint entering the current chunk from the future
+    float lam[NS];  // adjoint entering the current chunk from the future (kept by both halves)
 #pragma unroll
     for (int n = 0; n < NS; ++n)
       lam[n] = (p.dhT != nullptr && d_ok && n < p.N) ? p.dhT[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
     float dDsum = 0.f;
     uint32_t slab = 0;
     PROFB_INIT;
+    // dC / dB partial rows of the previous tile, written one tile late
+    float UV[NS];
+    int pend_t0 = 0, pend_len = 0;
+    uint32_t pend_par = 0;
+    bool pending = false;
+    auto flush_pending = [&]() {
+      if (!pending) return;
+      pending = false;
+      if (!mbar_wait(smem_u32(&bars.d5_full), pend_par)) timeout();
+      tc_fence_after();
+      if (half == 0) {  // carry part (U, V) + intra-chunk part, one row per step of the chunk
+        uint32_t x[16];
+        tmem_ld16_async(trow + (cid < 64 ? TM_DCI : TM_DBI), x);
+        tmem_ld_wait16(x);
+        const int tt = cid & 63;
+        if (tt < pend_len) {
+          float* dst = (cid < 64 ? p.dCpart : p.dBpart) +
+                       ((static_cast<int64_t>(b) * p.T + pend_t0 + tt) * p.ndt + dt) * NS;
+#pragma unroll
+          for (int q4 = 0; q4 < NS / 4; ++q4)
+            reinterpret_cast<float4*>(dst)[q4] =
+                make_float4(UV[4 * q4] + __uint_as_float(x[4 * q4]), UV[4 * q4 + 1] + __uint_as_float(x[4 * q4 + 1]),
+                            UV[4 * q4 + 2] + __uint_as_float(x[4 * q4 + 2]), UV[4 * q4 + 3] + __uint_as_float(x[4 * q4 + 3]));
+        }
+      }
+      tc_fence_before();
+    };
+
+    auto write_split_rows = [&](const float (&v)[NS], int c_hi, int c_lo) {
+      uint32_t hi[8], lo[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) split_bf16x2(v[2 * k], v[2 * k + 1], hi[k], lo[k]);
+      *reinterpret_cast<uint4*>(my_row + (c_hi + 0) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(my_row + (c_hi + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+      *reinterpret_cast<uint4*>(my_row + (c_lo + 0) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      *reinterpret_cast<uint4*>(my_row + (c_lo + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+    };
+
+    // checkpointed states of a chunk: xe = state at its end (seed of the r recurrence, both
+    // halves), hv = state entering it (first half only; h0 for the first chunk)
+    float xe[NS], hv[NS];
+    auto fetch_states = [&](int c) {
+      const int64_t tile = static_cast<int64_t>(c) * per_chunk + blockIdx.x;
+      const float4* src = reinterpret_cast<const float4*>(p.ckS + (tile * kDT + cid) * NS);
+#pragma unroll
+      for (int q4 = 0; q4 < NS / 4; ++q4) {
+        const float4 v = __ldg(src + q4);
+        xe[4 * q4] = v.x; xe[4 * q4 + 1] = v.y; xe[4 * q4 + 2] = v.z; xe[4 * q4 + 3] = v.w;
+      }
+      if (half == 0) {
+        if (c > 0) {
+          const float4* hs = reinterpret_cast<const float4*>(p.ckS + ((tile - per_chunk) * kDT + cid) * NS);
+#pragma unroll
+          for (int q4 = 0; q4 < NS / 4; ++q4) {
+            const float4 v = __ldg(hs + q4);
+            hv[4 * q4] = v.x; hv[4 * q4 + 1] = v.y; hv[4 * q4 + 2] = v.z; hv[4 * q4 + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < NS; ++n)
+            hv[n] = (p.h0 != nullptr && d_ok && n < p.N) ? p.h0[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
+        }
+      }
+    };
+    fetch_states(nchunks - 1);
 
     for (int it = 0; it < nchunks; ++it) {
       const int c = nchunks - 1 - it, t0 = c * Q, len = min(Q, p.T - t0);
       const uint32_t par = it & 1;
-      const int64_t tile = static_cast<int64_t>(c) * per_chunk + blockIdx.x;
-      // state entering the chunk and state at its end (both saved by the forward)
-      float4 hq[NS / 4], xq[NS / 4];
-      {
-        const float4* xe = reinterpret_cast<const float4*>(p.ckS + (tile * kDT + tid) * NS);
-#pragma unroll
-        for (int q4 = 0; q4 < NS / 4; ++q4) xq[q4] = __ldg(xe + q4);
-        if (c > 0) {
-          const float4* hs = reinterpret_cast<const float4*>(p.ckS + ((tile - per_chunk) * kDT + tid) * NS);
-#pragma unroll
-          for (int q4 = 0; q4 < NS / 4; ++q4) hq[q4] = __ldg(hs + q4);
-        } else {
-#pragma unroll
-          for (int q4 = 0; q4 < NS / 4; ++q4) {
-            float v[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int n = 4 * q4 + k;
-              v[k] = (p.h0 != nullptr && d_ok && n < p.N) ? p.h0[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
-            }
-            hq[q4] = make_float4(v[0], v[1], v[2], v[3]);
-          }
-        }
-      }
-
+      // xe / hv (state at the chunk end / entering the chunk) were fetched during the previous
+      // tile; the first half posts the h rows right away
+      if (half == 0) write_split_rows(hv, R_H1, R_H2);
       PROFB_MARK(0);
+
       // ---------------- gates: operand rows [al | wt] and the coefficients the epilogue needs
-      float R = 1.f, Rprev = 1.f;
+      float R = 1.f;
 #pragma unroll 1
-      for (int k = 0; k < NSLAB; ++k, ++slab) {
-        const uint32_t slot = slab % RING, ph = (slab / RING) & 1;
+      for (int k = 0; k < NSLAB; ++k) {
+        const uint32_t sidx = slab + k, slot = sidx % RING, ph = (sidx / RING) & 1;
+        const bool mine = (k >> 1) == half;
+        // (every thread waits for the slab before releasing it, needed or not: an arrival must
+        // not reach the empty barrier before its previous phase has completed)
         if (!mbar_wait(smem_u32(&bars.full[slot]), ph)) timeout();
+        if (half == 0 && !mine) {  // first half: slabs 2,3 are not needed
+          mbar_arrive(smem_u32(&bars.empty[slot]));
+          continue;
+        }
         const unsigned char* sl = smem + Smem::off_ring + slot * Smem::slab_bytes;
         const TA* s_u = reinterpret_cast<const TA*>(sl);
         const TA* s_fl = s_u + SLAB * kDT;
         const TA* s_il = s_fl + SLAB * kDT;
         const TA* s_dy = s_il + SLAB * kDT;
+        if (!mine) {
+          // second half on slabs 0,1: retention products only, to enter step 32 with R_32
+#pragma unroll
+          for (int tl = 0; tl < SLAB; ++tl) {
+            float a = fast_ex2(ld_as_f32(s_fl, tl * kDT + cid) * kNegLog2e);
+            if (k * SLAB + tl >= len) a = 0.f;
+            R *= 1.f + a;
+          }
+          mbar_arrive(smem_u32(&bars.empty[slot]));
+          continue;
+        }
+        float Rprev = R;
 #pragma unroll
         for (int j8 = 0; j8 < SLAB / 8; ++j8) {
           float wv[8], av[8];
@@ -388,10 +501,10 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int tl = 8 * j8 + j;
-            const float flv = ld_as_f32(s_fl, tl * kDT + tid);
-            const float ilv = fmaxf(ld_as_f32(s_il, tl * kDT + tid), -30.f);
-            const float uv = ld_as_f32(s_u, tl * kDT + tid);
-            const float dyv = ld_as_f32(s_dy, tl * kDT + tid);
+            const float flv = ld_as_f32(s_fl, tl * kDT + cid);
+            const float ilv = fmaxf(ld_as_f32(s_il, tl * kDT + cid), -30.f);
+            const float uv = ld_as_f32(s_u, tl * kDT + cid);
+            const float dyv = ld_as_f32(s_dy, tl * kDT + cid);
             float a = fast_ex2(flv * kNegLog2e);
             const float bq = fast_ex2(ilv * kNegLog2e);
             if (k * SLAB + tl >= len) a = 0.f;       // ragged last chunk: neutral step (f = 1)
@@ -428,97 +541,53 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 #undef NAJU_TST8
         }
         mbar_arrive(smem_u32(&bars.empty[slot]));
+        fence_async_smem();
+        mbar_arrive(smem_u32(&bars.part[k]));  // the time-contraction MMAs of this slab may go
       }
+      slab += NSLAB;
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       PROFB_MARK(1);
-      if (!(R < kRMax)) atomicOr(&p.hdr->status, NAJU_ST_DEEP_TILE);  // never expected here
-      const float PQ = fast_rcp(R);
-      {  // carry rows: h and lt = P_Q lam, two bf16 terms each
-        const float hv[NS] = {hq[0].x, hq[0].y, hq[0].z, hq[0].w, hq[1].x, hq[1].y, hq[1].z, hq[1].w,
-                              hq[2].x, hq[2].y, hq[2].z, hq[2].w, hq[3].x, hq[3].y, hq[3].z, hq[3].w};
-        uint32_t hi[8], lo[8];
+      if (half == 1) {
+        if (!(R < kRMax)) atomicOr(&p.hdr->status, NAJU_ST_DEEP_TILE);  // never expected here
+        const float PQ = fast_rcp(R);
+        s_PQ[cid] = PQ;
+        float lt[NS];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) split_bf16x2(hv[2 * k], hv[2 * k + 1], hi[k], lo[k]);
-        *reinterpret_cast<uint4*>(my_row + (R_H1 + 0) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(my_row + (R_H1 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-        *reinterpret_cast<uint4*>(my_row + (R_H2 + 0) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4*>(my_row + (R_H2 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) split_bf16x2(PQ * lam[2 * k], PQ * lam[2 * k + 1], hi[k], lo[k]);
-        *reinterpret_cast<uint4*>(my_row + (R_L1 + 0) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(my_row + (R_L1 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-        *reinterpret_cast<uint4*>(my_row + (R_L2 + 0) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        *reinterpret_cast<uint4*>(my_row + (R_L2 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        for (int n = 0; n < NS; ++n) lt[n] = PQ * lam[n];
+        write_split_rows(lt, R_L1, R_L2);
       }
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(&bars.rows_full));
-
+      mbar_arrive(smem_u32(&bars.carry_full));
+      flush_pending();  // previous tile's dC / dB rows, while this tile's MMAs run
       PROFB_MARK(2);
+
       // ---------------- epilogue
-      if (!mbar_wait(smem_u32(&bars.d_full), par)) timeout();
+      if (!mbar_wait(smem_u32(&bars.d1_full), par)) timeout();
       tc_fence_after();
       PROFB_MARK(3);
-      // cross-channel block first, so that the second MMA round overlaps the reverse sweep:
-      // threads t < 64 hold row t of [M2 | U | .], threads 64+s hold row s of [. | . | V]
-      float UV[NS];
-      {
-        uint32_t x[16];
-        if (tid < 64) {
-#pragma unroll
-          for (int s16 = 0; s16 < 4; ++s16) {
-            tmem_ld16_async(trow + TM_X + 16 * s16, x);
-            tmem_ld_wait16(x);
-            uint32_t hi[8], lo[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int s = 16 * s16 + 2 * k;
-              split_bf16x2(s <= tid ? __uint_as_float(x[2 * k]) : 0.f, s + 1 <= tid ? __uint_as_float(x[2 * k + 1]) : 0.f,
-                           hi[k], lo[k]);
-            }
-            unsigned char* mrow = smem + Smem::off_M + static_cast<uint32_t>(tid >> 3) * SBO_M + static_cast<uint32_t>(tid & 7) * 16;
-            *reinterpret_cast<uint4*>(mrow + (M_1 + 2 * s16) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(mrow + (M_1 + 2 * s16 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-            *reinterpret_cast<uint4*>(mrow + (M_2 + 2 * s16) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            *reinterpret_cast<uint4*>(mrow + (M_2 + 2 * s16 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-          }
-          tmem_ld16_async(trow + TM_X + 64, x);  // U[t, :]
-        } else {
-          tmem_ld16_async(trow + TM_X + 80, x);  // V[s, :]
-        }
-        tmem_ld_wait16(x);
-#pragma unroll
-        for (int n = 0; n < NS; ++n) UV[n] = __uint_as_float(x[n]);
-      }
-      fence_async_smem();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bars.m2_full));
-
-      PROFB_MARK(4);
       // adjoint leaving the chunk, and the seed of the r recurrence
       float rr = 0.f;
       {
         uint32_t dl[16];
         tmem_ld16_async(trow + TM_DL, dl);
         tmem_ld_wait16(dl);
-        const float xe[NS] = {xq[0].x, xq[0].y, xq[0].z, xq[0].w, xq[1].x, xq[1].y, xq[1].z, xq[1].w,
-                              xq[2].x, xq[2].y, xq[2].z, xq[2].w, xq[3].x, xq[3].y, xq[3].z, xq[3].w};
+        const float PQ = s_PQ[cid];
 #pragma unroll
         for (int n = 0; n < NS; ++n) {
           rr = fmaf(lam[n], xe[n], rr);
           lam[n] = fmaf(PQ, lam[n], __uint_as_float(dl[n]));
         }
       }
-
+      if (c > 0) fetch_states(c - 1);  // next tile's states: the loads fly during the sweep
       PROFB_MARK(5);
-      // reverse-time sweep: 8 steps per round, everything it needs comes from TMEM and this
+
+      // reverse-time sweep, 8 steps per round: everything it needs comes from TMEM and this
       // thread's own operand row
       unsigned char* out_u = smem + Smem::off_out;
       unsigned char* out_f = out_u + Q * kDT * 2;
       unsigned char* out_i = out_f + Q * kDT * 2;
       const TA* gdy = reinterpret_cast<const TA*>(p.dy) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d;
-      // TMEM loads are software-pipelined: round ch-1 is in flight while round ch is processed
-      uint32_t tq[2][5][8];
 #define NAJU_TLD8(COL, V, CH)                                                                                \
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"                       \
                : "=r"(V[0]), "=r"(V[1]), "=r"(V[2]), "=r"(V[3]), "=r"(V[4]), "=r"(V[5]), "=r"(V[6]), "=r"(V[7]) \
@@ -535,6 +604,40 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
                : "+r"(A[0]), "+r"(A[1]), "+r"(A[2]), "+r"(A[3]), "+r"(A[4]), "+r"(A[5]), "+r"(A[6]), "+r"(A[7]) \
                :                                                                                             \
                : "memory")
+      // TMEM loads are software-pipelined in both loops: the next round's columns are in flight
+      // while the current round is processed.
+      if (half == 0) {
+        // first half: r-increments of steps 63..32 only, to enter step 31 with r_32
+        uint32_t yq[2][8], gq[2][8];
+        NAJU_TLD8(TM_Y, yq[1], Q / 8 - 1);
+        NAJU_TLD8(TM_G, gq[1], Q / 8 - 1);
+        NAJU_TWAIT16(yq[1], gq[1]);
+#pragma unroll
+        for (int ch = Q / 8 - 1; ch >= Q / 16; --ch) {
+          const int cur = ch & 1, nxt = cur ^ 1;
+          if (ch > Q / 16) {
+            NAJU_TLD8(TM_Y, yq[nxt], ch - 1);
+            NAJU_TLD8(TM_G, gq[nxt], ch - 1);
+          }
+          const uint4 a1 = *reinterpret_cast<const uint4*>(my_row + (R_A1 + ch) * 128);
+          const uint4 a2 = *reinterpret_cast<const uint4*>(my_row + (R_A2 + ch) * 128);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(my_row + (R_W1 + ch) * 128);
+          const uint4 w2 = *reinterpret_cast<const uint4*>(my_row + (R_W2 + ch) * 128);
+          const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w}, a2w[4] = {a2.x, a2.y, a2.z, a2.w};
+          const uint32_t w1w[4] = {w1.x, w1.y, w1.z, w1.w}, w2w[4] = {w2.x, w2.y, w2.z, w2.w};
+#pragma unroll
+          for (int j = 7; j >= 0; --j) {
+            const uint32_t pa1 = a1w[j >> 1], pa2 = a2w[j >> 1], pw1 = w1w[j >> 1], pw2 = w2w[j >> 1];
+            const float al = (j & 1) ? bf16hi_f32(pa1) + bf16hi_f32(pa2) : bf16lo_f32(pa1) + bf16lo_f32(pa2);
+            const float wt = (j & 1) ? bf16hi_f32(pw1) + bf16hi_f32(pw2) : bf16lo_f32(pw1) + bf16lo_f32(pw2);
+            rr += fmaf(al, __uint_as_float(yq[cur][j]), -wt * __uint_as_float(gq[cur][j]));
+          }
+          if (ch > Q / 16) NAJU_TWAIT16(yq[nxt], gq[nxt]);
+        }
+      }
+      {
+        const int ch_hi = half ? Q / 8 - 1 : Q / 16 - 1;
+        uint32_t tq[2][5][8];
 #define NAJU_TLOAD_ROUND(BUF, CH)          \
   do {                                     \
     NAJU_TLD8(TM_Y, tq[BUF][0], CH);       \
@@ -549,46 +652,48 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     NAJU_TWAIT16(tq[BUF][2], tq[BUF][3]);      \
     NAJU_TWAIT8(tq[BUF][4]);                   \
   } while (0)
-      NAJU_TLOAD_ROUND(1, Q / 8 - 1);
-      NAJU_TWAIT_ROUND(1);
+        NAJU_TLOAD_ROUND(0, ch_hi);
+        NAJU_TWAIT_ROUND(0);
 #pragma unroll
-      for (int ch = Q / 8 - 1; ch >= 0; --ch) {
-        const int cur = ch & 1, nxt = cur ^ 1;
-        if (ch > 0) NAJU_TLOAD_ROUND(nxt, ch - 1);
-        const uint32_t* y8 = tq[cur][0];
-        const uint32_t* g8 = tq[cur][1];
-        const uint32_t* f8 = tq[cur][2];
-        const uint32_t* i8 = tq[cur][3];
-        const uint32_t* u8 = tq[cur][4];
-        const uint4 a1 = *reinterpret_cast<const uint4*>(my_row + (R_A1 + ch) * 128);
-        const uint4 a2 = *reinterpret_cast<const uint4*>(my_row + (R_A2 + ch) * 128);
-        const uint4 w1 = *reinterpret_cast<const uint4*>(my_row + (R_W1 + ch) * 128);
-        const uint4 w2 = *reinterpret_cast<const uint4*>(my_row + (R_W2 + ch) * 128);
-        const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w}, a2w[4] = {a2.x, a2.y, a2.z, a2.w};
-        const uint32_t w1w[4] = {w1.x, w1.y, w1.z, w1.w}, w2w[4] = {w2.x, w2.y, w2.z, w2.w};
+        for (int rd = 0; rd < Q / 16; ++rd) {
+          const int ch = ch_hi - rd;
+          const int cur = rd & 1, nxt = cur ^ 1;
+          if (rd + 1 < Q / 16) NAJU_TLOAD_ROUND(nxt, ch - 1);
+          const uint32_t* y8 = tq[cur][0];
+          const uint32_t* g8 = tq[cur][1];
+          const uint32_t* f8 = tq[cur][2];
+          const uint32_t* i8 = tq[cur][3];
+          const uint32_t* u8 = tq[cur][4];
+          const uint4 a1 = *reinterpret_cast<const uint4*>(my_row + (R_A1 + ch) * 128);
+          const uint4 a2 = *reinterpret_cast<const uint4*>(my_row + (R_A2 + ch) * 128);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(my_row + (R_W1 + ch) * 128);
+          const uint4 w2 = *reinterpret_cast<const uint4*>(my_row + (R_W2 + ch) * 128);
+          const uint32_t a1w[4] = {a1.x, a1.y, a1.z, a1.w}, a2w[4] = {a2.x, a2.y, a2.z, a2.w};
+          const uint32_t w1w[4] = {w1.x, w1.y, w1.z, w1.w}, w2w[4] = {w2.x, w2.y, w2.z, w2.w};
 #pragma unroll
-        for (int j = 7; j >= 0; --j) {
-          const int t = 8 * ch + j;
-          const uint32_t pa1 = a1w[j >> 1], pa2 = a2w[j >> 1], pw1 = w1w[j >> 1], pw2 = w2w[j >> 1];
-          const float al = (j & 1) ? bf16hi_f32(pa1) + bf16hi_f32(pa2) : bf16lo_f32(pa1) + bf16lo_f32(pa2);
-          const float wt = (j & 1) ? bf16hi_f32(pw1) + bf16hi_f32(pw2) : bf16lo_f32(pw1) + bf16lo_f32(pw2);
-          const float yt = __uint_as_float(y8[j]), gt = __uint_as_float(g8[j]);
-          rr += fmaf(al, yt, -wt * gt);
-          const float dfl = __uint_as_float(f8[j]) * rr;
-          float du = __uint_as_float(u8[j]) * gt;
-          if (Dv != 0.f && t < len) du = fmaf(Dv, to_f32(gdy[static_cast<int64_t>(t) * p.D]), du);
-          const float dil = wt * __uint_as_float(i8[j]) * gt;
-          reinterpret_cast<TA*>(out_u)[t * kDT + tid] = from_f32<TA>(du);
-          reinterpret_cast<TA*>(out_f)[t * kDT + tid] = from_f32<TA>(dfl);
-          reinterpret_cast<TA*>(out_i)[t * kDT + tid] = from_f32<TA>(dil);
+          for (int j = 7; j >= 0; --j) {
+            const int t = 8 * ch + j;
+            const uint32_t pa1 = a1w[j >> 1], pa2 = a2w[j >> 1], pw1 = w1w[j >> 1], pw2 = w2w[j >> 1];
+            const float al = (j & 1) ? bf16hi_f32(pa1) + bf16hi_f32(pa2) : bf16lo_f32(pa1) + bf16lo_f32(pa2);
+            const float wt = (j & 1) ? bf16hi_f32(pw1) + bf16hi_f32(pw2) : bf16lo_f32(pw1) + bf16lo_f32(pw2);
+            const float yt = __uint_as_float(y8[j]), gt = __uint_as_float(g8[j]);
+            rr += fmaf(al, yt, -wt * gt);
+            const float dfl = __uint_as_float(f8[j]) * rr;
+            float du = __uint_as_float(u8[j]) * gt;
+            if (Dv != 0.f && t < len) du = fmaf(Dv, to_f32(gdy[static_cast<int64_t>(t) * p.D]), du);
+            const float dil = wt * __uint_as_float(i8[j]) * gt;
+            reinterpret_cast<TA*>(out_u)[t * kDT + cid] = from_f32<TA>(du);
+            reinterpret_cast<TA*>(out_f)[t * kDT + cid] = from_f32<TA>(dfl);
+            reinterpret_cast<TA*>(out_i)[t * kDT + cid] = from_f32<TA>(dil);
+          }
+          if (rd + 1 < Q / 16) NAJU_TWAIT_ROUND(nxt);
         }
-        if (ch > 0) NAJU_TWAIT_ROUND(nxt);
+#undef NAJU_TLOAD_ROUND
+#undef NAJU_TWAIT_ROUND
       }
 #undef NAJU_TLD8
 #undef NAJU_TWAIT16
 #undef NAJU_TWAIT8
-#undef NAJU_TLOAD_ROUND
-#undef NAJU_TWAIT_ROUND
       PROFB_MARK(6);
       tc_fence_before();
       bar_sync<1, NMAIN>();
@@ -608,33 +713,62 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           }
         }
       }
+      bar_sync<1, NMAIN>();  // staging fully read before the M2 operand overwrites part of it
       PROFB_MARK(7);
-      // dC / dB partial rows of this channel tile: carry part (U, V) + intra-chunk part
-      if (!mbar_wait(smem_u32(&bars.d5_full), par)) timeout();
+
+      // ---------------- cross-channel block (its MMAs ran during the sweep): lanes t < 64 hold row t
+      // of [M2 | U | .], lanes 64+s hold row s of [. | . | V]
+      if (!mbar_wait(smem_u32(&bars.d4_full), par)) timeout();
       tc_fence_after();
       {
         uint32_t x[16];
-        tmem_ld16_async(trow + (tid < 64 ? TM_DCI : TM_DBI), x);
-        tmem_ld_wait16(x);
-        const int tt = tid & 63;
-        if (tt < len) {
-          float* dst = (tid < 64 ? p.dCpart : p.dBpart) +
-                       ((static_cast<int64_t>(b) * p.T + t0 + tt) * p.ndt + dt) * NS;
+        if (cid < 64) {
+          // masked M2 row t as a two-term bf16 operand; each half writes 32 of the 64 columns
 #pragma unroll
-          for (int q4 = 0; q4 < NS / 4; ++q4)
-            reinterpret_cast<float4*>(dst)[q4] =
-                make_float4(UV[4 * q4] + __uint_as_float(x[4 * q4]), UV[4 * q4 + 1] + __uint_as_float(x[4 * q4 + 1]),
-                            UV[4 * q4 + 2] + __uint_as_float(x[4 * q4 + 2]), UV[4 * q4 + 3] + __uint_as_float(x[4 * q4 + 3]));
+          for (int q2 = 0; q2 < 2; ++q2) {
+            const int s16 = 2 * half + q2;
+            tmem_ld16_async(trow + TM_X + 16 * s16, x);
+            tmem_ld_wait16(x);
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int s = 16 * s16 + 2 * k;
+              split_bf16x2(s <= cid ? __uint_as_float(x[2 * k]) : 0.f, s + 1 <= cid ? __uint_as_float(x[2 * k + 1]) : 0.f,
+                           hi[k], lo[k]);
+            }
+            unsigned char* mrow = smem + Smem::off_M + static_cast<uint32_t>(cid >> 3) * SBO_M + static_cast<uint32_t>(cid & 7) * 16;
+            *reinterpret_cast<uint4*>(mrow + (M_1 + 2 * s16) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(mrow + (M_1 + 2 * s16 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+            *reinterpret_cast<uint4*>(mrow + (M_2 + 2 * s16) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4*>(mrow + (M_2 + 2 * s16 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+          }
+        }
+        if (half == 0) {
+          tmem_ld16_async(trow + TM_X + (cid < 64 ? 64 : 80), x);  // U[t,:] or V[s,:]
+          tmem_ld_wait16(x);
+#pragma unroll
+          for (int n = 0; n < NS; ++n) UV[n] = __uint_as_float(x[n]);
         }
       }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars.m2_full));
+      PROFB_MARK(4);
+      // The second MMA round (intra-chunk parts of dC / dB) is not waited for here: its result is
+      // picked up while the next tile waits for its own first round.
+      pend_t0 = t0;
+      pend_len = len;
+      pend_par = par;
+      pending = true;
       tc_fence_before();
       mbar_arrive(smem_u32(&bars.tile_done));
       bar_sync<1, NMAIN>();  // rows, output staging and TMEM are free for the next tile
       PROFB_MARK(8);
     }
-    // tile (b, dt) is done: per-row D_skip partial and the gradient of the initial state
-    p.dDpart[static_cast<int64_t>(b) * (p.ndt * kDT) + d0 + tid] = dDsum;
-    if (p.dh0 != nullptr && d_ok) {
+    flush_pending();
+    // channel tile done: D_skip partials (one row per half and batch row), gradient of h0
+    p.dDpart[(static_cast<int64_t>(half) * p.B + b) * (p.ndt * kDT) + d0 + cid] = dDsum;
+    if (half == 0 && p.dh0 != nullptr && d_ok) {
       float* o = p.dh0 + (static_cast<int64_t>(b) * p.D + d) * p.N;
 #pragma unroll
       for (int n = 0; n < NS; ++n)
