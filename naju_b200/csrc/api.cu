@@ -138,6 +138,8 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   p.aggP = reinterpret_cast<float*>(sc + sl.off_aggP);
   p.aggS = reinterpret_cast<float*>(sc + sl.off_aggS);
   if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY)) {
+    const int rc3 = launch_fwd_tc3(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
+    if (rc3 != -1000) return rc3;
     const int rc2 = launch_fwd_tc2(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
     if (rc2 != -1000) return rc2;
     if (fwd_tc_supported(g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype))

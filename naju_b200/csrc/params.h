@@ -145,6 +145,9 @@ int launch_fwd_tc(const FwdParams& p, const Geometry& g, int act_dtype, int gate
 // TMA-fed persistent tensor-core forward; returns -1000 when the problem cannot take it
 int launch_fwd_tc2(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype,
                    void* stream);
+// walk-along-time tensor-core forward (two threads per channel); -1000 when it cannot take the problem
+int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype,
+                   void* stream);
 int launch_bwd_simt(const BwdParams& p, const Geometry& g, int act_dtype, int gate_dtype,
                     void* dB, void* dC, float* dD, void* stream);
 // tensor-core backward; returns -1000 when the problem cannot take it
