@@ -148,6 +148,16 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def ncu_traffic_bwd(B, T, D, N):
+    """DRAM bytes of one tensor-core backward launch, from the ncu capture summarised in
+    profiles/tensor_core_kernels_B8_T2048_D2048_N16.md: 496.3 MB for 16384 tokens at D=2048, N=16
+    (dram__bytes.sum.per_second x gpu__time_duration).  Traffic grows in proportion to the tokens
+    (every tile moves the same bytes), so a full launch is that figure scaled by the token count."""
+    if (D, N) != (2048, 16):
+        return None
+    return 496.3e6 / 16384.0 * (B * T)
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_gpu_arm(args):
     import torch
@@ -286,15 +296,17 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
                        f"scan fwd+bwd B={B} T={T} D={D} N={N} per GPU",
                        "io_dtype": "bf16", "state_dtype": "f32", "sharding": f"batch x{world}, no collective",
                        "l2": "inputs larger than L2 (no flush needed)",
+                       "d_skip": "zeros, as the mixer passes them (the skip is applied outside the scan)",
                        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                        "fwd_gbs": fwd_bytes / (fwd_ms / 1e3) / 1e9,
                        "fwd_bwd_gbs": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9,
                        "fwd_bwd_frac_of_peak": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9 / peak},
             "roofline": {"bound": "hbm", "kernel": "bwd_tc_kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak, "traffic": ncu_traffic_bwd(B, T, D, N),
                          "algorithmic_bytes_per_launch": bwd_bytes},
-            "gpu_launches": 6 * args.steps,  # fwd_tc2 + bwd_tc + bwd_simt (stands down) + 3 finalize
+            # forward + tensor-core backward + recurrent backward (stands down) + 3 finalize kernels
+            "gpu_launches": 6 * args.steps,
             "clocks": clocks,
         }
         if e2e_steps:
