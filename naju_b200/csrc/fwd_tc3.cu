@@ -28,7 +28,8 @@
 //   warps 0-7   carry/epilogue warps: warps 0-3 turn D2 into the next chunk's carry-in (registers),
 //               write the checkpoint and post the carry-in row one tile ahead; all eight read
 //               y_t = P_t D1[d][t] back from TMEM (lane = channel, 16 / 48 columns per thread),
-//               stage it in shared memory and write it with 16-byte stores.
+//               add D_skip u_t (u is kept in shared memory for this), stage the tile in shared
+//               memory and hand it to a TMA store.
 // A tile whose retention product falls below 2^-80 in any channel (deep gates) cannot use the
 // 1/P_t factorisation; warps 0-3 then run the exact recurrence for that tile straight from global
 // memory, from the carry they hold.  Every wait is bounded.
@@ -86,14 +87,18 @@ __device__ unsigned long long g_prof[48];
 #endif
 
 struct Maps {
-  CUtensorMap u, fl, il, bm, cm;
+  CUtensorMap u, fl, il, bm, cm, y;
 };
 
 template <typename TG>
 struct Smem {
-  static constexpr uint32_t slab_bytes = SLAB * kDT * (2 + 2 * sizeof(TG));
+  static constexpr uint32_t slab_bytes = SLAB * kDT * (2 + 2 * sizeof(TG));  // u, f_logit, i_logit
+  // With 16-bit logits there is room to keep a second copy of the tile's u for the epilogue
+  // (D_skip u_t); with fp32 logits the epilogue reads u from global memory instead.
+  static constexpr bool kStashU = sizeof(TG) == 2;
   static constexpr uint32_t off_ring = 0;
-  static constexpr uint32_t off_AW = off_ring + RING * slab_bytes;  // [NSTAGE]
+  static constexpr uint32_t off_U = off_ring + RING * slab_bytes;                      // [NSTAGE][Q][128]
+  static constexpr uint32_t off_AW = off_U + (kStashU ? NSTAGE * Q * kDT * 2 : 0);     // [NSTAGE]
   static constexpr uint32_t off_AH = off_AW + NSTAGE * AW_BYTES;
   static constexpr uint32_t off_B1 = off_AH + AH_BYTES;             // [NSTAGE]
   static constexpr uint32_t off_B2 = off_B1 + NSTAGE * B1_BYTES;    // [NSTAGE]
@@ -103,6 +108,7 @@ struct Smem {
 
 struct Bars {
   unsigned long long full[RING], empty[RING];   // input slabs (producer -> gate warps)
+  unsigned long long u_full[NSTAGE];            // the epilogue's copy of the tile's u has landed
   unsigned long long bc_full[2], bc_empty[2];   // raw B/C rows per tile parity
   unsigned long long part[NSTAGE][NSLAB];       // operand-row chunks of one slab written (128 threads)
   unsigned long long a_full[NSTAGE];            // all gate threads done with the tile (P_t in TMEM, flags)
@@ -183,6 +189,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     for (int i = 0; i < NSTAGE; ++i) {
       for (int k = 0; k < NSLAB; ++k) mbar_init(smem_u32(&bars.part[i][k]), NHALF);
       mbar_init(smem_u32(&bars.a_full[i]), NGATE);
+      mbar_init(smem_u32(&bars.u_full[i]), 1);
       mbar_init(smem_u32(&bars.ops_full[i]), 1);
       mbar_init(smem_u32(&bars.d2_full[i]), 1);
       mbar_init(smem_u32(&bars.stage_free[i]), NEPI);
@@ -208,10 +215,27 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     if (lane == 0) {
       uint32_t slab = 0;
       int it = 0;
+      // The epilogue's copy of tile j's u goes to the stage buffer once the tile two back has left
+      // it; it is requested one tile late, where waiting for that cannot hold up any other load.
+      int pb = 0, pd0 = 0, pt0 = 0;
+      auto load_u_copy = [&](int j) {
+        if constexpr (SM::kStashU) {
+          const int st = j & 1;
+          if (j >= NSTAGE && !mbar_wait(smem_u32(&bars.stage_free[st]), ((j >> 1) & 1) ^ 1)) timeout();
+          const uint32_t bar = smem_u32(&bars.u_full[st]);
+          mbar_arrive_expect_tx(bar, Q * kDT * 2);
+          for (int k = 0; k < NSLAB; ++k)
+            tma_load_3d(sbase + SM::off_U + st * Q * kDT * 2 + k * SLAB * kDT * 2, &maps.u, pd0, pt0 + k * SLAB, pb, bar);
+        }
+      };
       for (int x = x_first; x < ctiles; x += x_step) {
         const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
         for (int c = 0; c < nchunks; ++c, ++it) {
           const int t0 = c * Q;
+          if (it >= 1) load_u_copy(it - 1);
+          pb = b;
+          pd0 = d0;
+          pt0 = t0;
           if (it >= 2 && !mbar_wait(smem_u32(&bars.bc_empty[it & 1]), ((it >> 1) & 1) ^ 1)) timeout();
           {
             const uint32_t bar = smem_u32(&bars.bc_full[it & 1]);
@@ -232,6 +256,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
         }
       }
+      if (it >= 1) load_u_copy(it - 1);
     }
   } else if (warp == 17) {
     // ===================================================================== operand builder
@@ -379,9 +404,17 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           const TG* s_fl = reinterpret_cast<const TG*>(sl + SLAB * kDT * 2) + q;
           const TG* s_il = s_fl + SLAB * kDT;
           if (!mine) {
-            if (half == 1) {  // second thread on slabs 0,1: retention products only
-#pragma unroll 4
-              for (int tl = 0; tl < SLAB; ++tl) R *= 1.f + fast_ex2(ld_as_f32(s_fl, tl * kDT) * kNegLog2e);
+            if (half == 1) {
+              // second thread on slabs 0,1: retention products only.  The sixteen factors are
+              // independent: multiply them as a tree, not as a chain.
+              float fac[SLAB];
+#pragma unroll
+              for (int tl = 0; tl < SLAB; ++tl) fac[tl] = 1.f + fast_ex2(ld_as_f32(s_fl, tl * kDT) * kNegLog2e);
+#pragma unroll
+              for (int w = SLAB / 2; w >= 1; w >>= 1)
+#pragma unroll
+                for (int i = 0; i < w; ++i) fac[i] *= fac[i + w];
+              R *= fac[0];
             }
             mbar_arrive(smem_u32(&bars.empty[slot]));
             continue;
@@ -531,7 +564,11 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         // stage (step t -> 256 contiguous bytes), written out with 16-byte stores
         unsigned char* ystage = smem + SM::off_AW + st * AW_BYTES;
         if (!deep) {
+          const TA* s_u = reinterpret_cast<const TA*>(smem + SM::off_U + st * Q * kDT * 2) + q;
           const TA* gu = reinterpret_cast<const TA*>(p.u) + tcd.b * p.u_sb + static_cast<int64_t>(tcd.t0) * p.u_st + tcd.d;
+          if constexpr (SM::kStashU) {
+            if (!mbar_wait(smem_u32(&bars.u_full[st]), (it >> 1) & 1)) timeout();
+          }
           const int c_lo = half ? EPI_A_COLS : 0;
           const int nblk = half ? (Q - EPI_A_COLS) / 8 : EPI_A_COLS / 8;
           uint32_t vA[8], pA[8], vB[8], pB[8];
@@ -543,8 +580,13 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
               float y0 = __uint_as_float(pt[k]) * __uint_as_float(v[k]);
               float y1 = __uint_as_float(pt[k + 1]) * __uint_as_float(v[k + 1]);
               if (Dv != 0.f) {
-                if (t < len) y0 = fmaf(Dv, to_f32(gu[static_cast<int64_t>(t) * p.u_st]), y0);
-                if (t + 1 < len) y1 = fmaf(Dv, to_f32(gu[static_cast<int64_t>(t + 1) * p.u_st]), y1);
+                if constexpr (SM::kStashU) {  // (u past the end of the sequence is zero)
+                  y0 = fmaf(Dv, ld_as_f32(s_u, t * kDT), y0);
+                  y1 = fmaf(Dv, ld_as_f32(s_u, (t + 1) * kDT), y1);
+                } else {
+                  if (t < len) y0 = fmaf(Dv, to_f32(gu[static_cast<int64_t>(t) * p.u_st]), y0);
+                  if (t + 1 < len) y1 = fmaf(Dv, to_f32(gu[static_cast<int64_t>(t + 1) * p.u_st]), y1);
+                }
               }
               unsigned short o0, o1;
               if constexpr (std::is_same<TA, __nv_bfloat16>::value) {
@@ -579,25 +621,23 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
         }
         PROF_MARK(8 * half + 4);
+        fence_async_smem();
         tc_fence_before();
         bar_sync<1, NEPI>();
         PROF_MARK(8 * half + 5);
-        if (!deep) {
-          TA* gy = reinterpret_cast<TA*>(p.y) + (static_cast<int64_t>(tcd.b) * p.T + tcd.t0) * p.D + tcd.d0;
-#pragma unroll
-          for (int i = 0; i < (Q * kDT * 2 / 16) / NEPI; ++i) {
-            const int v16 = i * NEPI + tid, t = v16 >> 4, c16 = v16 & 15;
-            if (t < len && c16 * 8 < tcd.cols) {
-              const uint4 val = *reinterpret_cast<const uint4*>(ystage + (t >> 3) * SBO_AW + (t & 7) * 256 + c16 * 16);
-              *reinterpret_cast<uint4*>(gy + static_cast<int64_t>(t) * p.D + c16 * 8) = val;
-            }
-          }
+        if (!deep && tid == 0) {
+          // the staged tile leaves by TMA (steps past T and channels past D are clipped); the stage
+          // is released once the store has read it
+          tma_store_3d(&maps.y, tcd.d0, tcd.t0, tcd.b, smem_u32(ystage));
+          tma_store_commit();
+          tma_store_wait_read();
         }
         mbar_arrive(smem_u32(&bars.stage_free[st]));
         PROF_MARK(8 * half + 6);
       }
     }
   }
+  if (tid == 0) tma_store_wait_all();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
@@ -699,7 +739,8 @@ int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act, int gate, int
       make_map3(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tc3::SLAB) &&
       make_map3(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tc3::SLAB) &&
       make_map3(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tc3::NS, tc3::Q) &&
-      make_map3(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tc3::NS, tc3::Q);
+      make_map3(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tc3::NS, tc3::Q) &&
+      make_map3(&maps.y, p.y, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tc3::Q);
   if (!ok) return -1000;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (act == NAJU_BF16 && gate == NAJU_BF16) return launch_tc3_t<__nv_bfloat16, __nv_bfloat16>(p, g, maps, st);

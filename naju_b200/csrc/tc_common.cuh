@@ -107,6 +107,12 @@ __device__ __forceinline__ void tmem_ld_wait8(uint32_t (&a)[8], uint32_t (&b)[8]
                :
                : "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait8(uint32_t (&a)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7])
+               :
+               : "memory");
+}
 
 // ---- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t count) {
@@ -158,6 +164,20 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
       ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(mbar)
       : "memory");
 }
+
+// 3-D tiled store shared -> global (bulk async-group completion).  The writers of the shared tile
+// fence (fence_async_smem) and synchronise before one thread issues the store; rows and columns
+// of the box that fall outside the tensor are not written.  Same 16-byte rule as the load.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t smem_src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all earlier store groups of this thread have finished READING shared memory (the tile may be reused)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all earlier store groups of this thread are complete (before the kernel exits)
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- named barrier over a subset of the CTA's warps
 template <int ID, int COUNT>
