@@ -99,20 +99,32 @@ struct Maps {
   CUtensorMap u, fl, il, dy, bm, cm;
 };
 
-struct Smem {
-  static constexpr uint32_t slab_bytes = SLAB * kDT * 2 * 4;  // u, fl, il, dy (all 16-bit)
+// TG = type of the logits and of their gradients.  With 16-bit logits all three output tiles are
+// staged in shared memory and written with 16-byte stores; with fp32 logits the input slabs are
+// larger, only du is staged, and d f_logit / d i_logit go out straight from registers (a warp's
+// 32 consecutive fp32 values are a full 128-byte line).
+template <typename TG>
+struct SmemT {
+  static constexpr bool kStageGates = sizeof(TG) == 2;
+  static constexpr uint32_t off_sfl = SLAB * kDT * 2;                       // slab: u | fl | il | dy
+  static constexpr uint32_t off_sil = off_sfl + SLAB * kDT * sizeof(TG);
+  static constexpr uint32_t off_sdy = off_sil + SLAB * kDT * sizeof(TG);
+  static constexpr uint32_t slab_bytes = off_sdy + SLAB * kDT * 2;
   static constexpr uint32_t off_ring = 0;
   static constexpr uint32_t off_rows = off_ring + RING * slab_bytes;
-  static constexpr uint32_t off_BG = off_rows + ROWS_BYTES;
+  static constexpr uint32_t off_out = off_rows + ROWS_BYTES;      // du | dfl | dil staging, [64][128] each
+  // The M2 operand re-uses the du staging tile: it is written after the staged outputs have been
+  // stored and consumed (second MMA round) before the next sweep stages anything.  As an MMA
+  // operand it is addressed as 128 rows (32 KB) although only 64 exist, so at least 16 KB of
+  // shared memory must follow it: the staging tiles come before the shared operand buffers.
+  static constexpr uint32_t off_M = off_out;
+  static constexpr uint32_t off_BG = off_out + (kStageGates ? 3 : 1) * Q * kDT * 2;
   static constexpr uint32_t off_BB = off_BG + BG_BYTES;
   static constexpr uint32_t off_CT = off_BB + BB_BYTES;
   static constexpr uint32_t off_BT = off_CT + T_BYTES;
   static constexpr uint32_t off_bc = off_BT + T_BYTES;            // [2 tiles][B raw | C raw]
-  static constexpr uint32_t off_out = off_bc + 2 * 2 * BC_BYTES;  // du | dfl | dil, [64][128] each
-  // The M2 operand re-uses the du staging tile: it is written after the staged outputs have been
-  // stored and consumed (second MMA round) before the next sweep stages anything.
-  static constexpr uint32_t off_M = off_out;
-  static constexpr uint32_t total = off_out + 3 * Q * kDT * 2;
+  static constexpr uint32_t total = off_bc + 2 * 2 * BC_BYTES;
+  static_assert(off_M + 16 * SBO_M <= total, "the 128-row view of the M2 operand must stay inside shared memory");
 };
 
 struct Bars {
@@ -125,10 +137,10 @@ struct Bars {
   unsigned long long d1_full, d4_full, m2_full, d5_full, tile_done;
 };
 
-template <typename TA>
+template <typename TA, typename TG>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* __restrict__ fwd_form) {
-  (void)0;
+  using Smem = SmemT<TG>;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ Bars bars;
   __shared__ unsigned int s_tmem;
@@ -196,9 +208,9 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           const uint32_t dst = sbase + Smem::off_ring + slot * Smem::slab_bytes;
           mbar_arrive_expect_tx(bar, Smem::slab_bytes);
           tma_load_3d(dst, &maps.u, d0, t0 + k * SLAB, b, bar);
-          tma_load_3d(dst + SLAB * kDT * 2, &maps.fl, d0, t0 + k * SLAB, b, bar);
-          tma_load_3d(dst + SLAB * kDT * 4, &maps.il, d0, t0 + k * SLAB, b, bar);
-          tma_load_3d(dst + SLAB * kDT * 6, &maps.dy, d0, t0 + k * SLAB, b, bar);
+          tma_load_3d(dst + Smem::off_sfl, &maps.fl, d0, t0 + k * SLAB, b, bar);
+          tma_load_3d(dst + Smem::off_sil, &maps.il, d0, t0 + k * SLAB, b, bar);
+          tma_load_3d(dst + Smem::off_sdy, &maps.dy, d0, t0 + k * SLAB, b, bar);
         }
       }
     }
@@ -479,9 +491,9 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
         const unsigned char* sl = smem + Smem::off_ring + slot * Smem::slab_bytes;
         const TA* s_u = reinterpret_cast<const TA*>(sl);
-        const TA* s_fl = s_u + SLAB * kDT;
-        const TA* s_il = s_fl + SLAB * kDT;
-        const TA* s_dy = s_il + SLAB * kDT;
+        const TG* s_fl = reinterpret_cast<const TG*>(sl + Smem::off_sfl);
+        const TG* s_il = reinterpret_cast<const TG*>(sl + Smem::off_sil);
+        const TA* s_dy = reinterpret_cast<const TA*>(sl + Smem::off_sdy);
         if (!mine) {
           // second half on slabs 0,1: retention products only, to enter step 32 with R_32
 #pragma unroll
@@ -588,6 +600,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       unsigned char* out_f = out_u + Q * kDT * 2;
       unsigned char* out_i = out_f + Q * kDT * 2;
       const TA* gdy = reinterpret_cast<const TA*>(p.dy) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d;
+      TG* gdfl = reinterpret_cast<TG*>(p.dfl) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d;
+      TG* gdil = reinterpret_cast<TG*>(p.dil) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d;
 #define NAJU_TLD8(COL, V, CH)                                                                                \
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"                       \
                : "=r"(V[0]), "=r"(V[1]), "=r"(V[2]), "=r"(V[3]), "=r"(V[4]), "=r"(V[5]), "=r"(V[6]), "=r"(V[7]) \
@@ -683,8 +697,13 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
             if (Dv != 0.f && t < len) du = fmaf(Dv, to_f32(gdy[static_cast<int64_t>(t) * p.D]), du);
             const float dil = wt * __uint_as_float(i8[j]) * gt;
             reinterpret_cast<TA*>(out_u)[t * kDT + cid] = from_f32<TA>(du);
-            reinterpret_cast<TA*>(out_f)[t * kDT + cid] = from_f32<TA>(dfl);
-            reinterpret_cast<TA*>(out_i)[t * kDT + cid] = from_f32<TA>(dil);
+            if constexpr (Smem::kStageGates) {
+              reinterpret_cast<TG*>(out_f)[t * kDT + cid] = from_f32<TG>(dfl);
+              reinterpret_cast<TG*>(out_i)[t * kDT + cid] = from_f32<TG>(dil);
+            } else if (d_ok && t < len) {
+              gdfl[static_cast<int64_t>(t) * p.D] = from_f32<TG>(dfl);
+              gdil[static_cast<int64_t>(t) * p.D] = from_f32<TG>(dil);
+            }
           }
           if (rd + 1 < Q / 16) NAJU_TWAIT_ROUND(nxt);
         }
@@ -702,7 +721,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         TA* gout[3] = {reinterpret_cast<TA*>(p.du) + goff, reinterpret_cast<TA*>(p.dfl) + goff,
                        reinterpret_cast<TA*>(p.dil) + goff};
 #pragma unroll
-        for (int w3 = 0; w3 < 3; ++w3) {
+        for (int w3 = 0; w3 < (Smem::kStageGates ? 3 : 1); ++w3) {
           const unsigned char* src = out_u + w3 * (Q * kDT * 2);
 #pragma unroll
           for (int i = 0; i < (Q * kDT * 2 / 16) / NMAIN; ++i) {
@@ -816,7 +835,7 @@ EncodeFn encode_fn_b() {
 
 bool make_map_b(CUtensorMap* m, const void* base, int dt, int64_t B, int64_t T, int64_t inner, int64_t sb,
                 int64_t st, int box_inner, int box_t) {
-  const int es = 2;
+  const int es = dt == NAJU_F32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
   if ((st * es) % 16 != 0 || (sb * es) % 16 != 0 || (box_inner * es) % 16 != 0) return false;
   if (B > 1 && sb < st) return false;
@@ -826,7 +845,10 @@ bool make_map_b(CUtensorMap* m, const void* base, int dt, int64_t B, int64_t T, 
   cuuint32_t estr[3] = {1, 1, 1};
   EncodeFn fn = encode_fn_b();
   if (!fn) return false;
-  return fn(m, dt == NAJU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  return fn(m,
+            dt == NAJU_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : (dt == NAJU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
+            3,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -847,9 +869,23 @@ int sm_count_b() {
 
 // Launches the tensor-core backward for this problem if it can take it; returns -1000 if not.
 // The kernel itself stands down unless *fwd_form says the forward ran chunked without deep tiles.
+namespace {
+template <typename TA, typename TG>
+int launch_bwd_tc_t(const BwdParams& p, const tcb::Maps& maps, const int* fwd_form, int64_t ctiles, cudaStream_t st) {
+  auto kern = tcb::bwd_tc_kernel<TA, TG>;
+  constexpr size_t smem = tcb::SmemT<TG>::total;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kern<<<static_cast<unsigned>(ctiles), tcb::NTHREADS, smem, st>>>(p, maps, fwd_form);
+  return static_cast<int>(cudaGetLastError());
+}
+}  // namespace
+
 int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int bc, const int* fwd_form,
                   void* stream) {
-  if (!(g.N == tcb::NS && g.TC == tcb::Q && act == NAJU_BF16 && gate == NAJU_BF16 && bc == NAJU_BF16)) return -1000;
+  if (!(g.N == tcb::NS && g.TC == tcb::Q && act == NAJU_BF16 && (gate == NAJU_BF16 || gate == NAJU_F32) &&
+        bc == NAJU_BF16))
+    return -1000;
   const int64_t ctiles = static_cast<int64_t>(g.B) * g.ndt;
   if (!(ctiles * 2 >= sm_count_b() && ctiles <= sm_count_b() && g.nchunks >= 4)) return -1000;
   tcb::Maps maps;
@@ -861,13 +897,9 @@ int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int 
       make_map_b(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tcb::NS, tcb::Q) &&
       make_map_b(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q);
   if (!ok) return -1000;
-  auto kern = tcb::bwd_tc_kernel<__nv_bfloat16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(tcb::Smem::total));
-  if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<static_cast<unsigned>(ctiles), tcb::NTHREADS, tcb::Smem::total, static_cast<cudaStream_t>(stream)>>>(
-      p, maps, fwd_form);
-  return static_cast<int>(cudaGetLastError());
+  if (gate == NAJU_F32)
+    return launch_bwd_tc_t<__nv_bfloat16, float>(p, maps, fwd_form, ctiles, static_cast<cudaStream_t>(stream));
+  return launch_bwd_tc_t<__nv_bfloat16, __nv_bfloat16>(p, maps, fwd_form, ctiles, static_cast<cudaStream_t>(stream));
 }
 
 }  // namespace naju

@@ -184,6 +184,40 @@ def test_tensor_core_chunked_backward(case):
         assert oracle.rel_l2(t["h0"].grad.cpu().numpy(), g["dh0"]) < 1e-4
 
 
+@pytest.mark.parametrize("case", [(4, 256, 2432, 16, 2.0, True), (4, 520, 2432, 16, 4.0, False)])
+def test_tensor_core_fp32_logits(case):
+    """The mixer's dtype mix under bf16 autocast (bf16 u, B, C; fp32 logits and logit gradients)
+    through the tensor-core forward and backward: the logits are not quantised, their gradients
+    come back in fp32 and carry no output rounding, so they show the arithmetic error (the 2e-3
+    gradient tolerance of the build; measured ~1e-5)."""
+    from naju_b200 import naju_scan
+    B, T, D, N, fs, state = case
+    dt = torch.bfloat16
+    d = oracle.make_inputs(B, T, D, N, seed=5, f_shift=fs, d_skip_scale=0.01, with_h0=True)
+    q = {k: (_round(d[k], dt) if k in ("u", "Bm", "Cm", "dy") else d[k]) for k in d}
+    t = {k: torch.tensor(q[k], device="cuda").to(dt if k in ("u", "Bm", "Cm") else torch.float32).requires_grad_(True)
+         for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "h0")}
+    if state:
+        y, hT = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"], h0=t["h0"], return_final_state=True)
+        torch.autograd.backward([y, hT], [torch.tensor(q["dy"], device="cuda").to(dt), torch.tensor(d["dhT"], device="cuda")])
+    else:
+        y = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"])
+        y.backward(torch.tensor(q["dy"], device="cuda").to(dt))
+    torch.cuda.synchronize()
+    assert t["fl"].grad.dtype == torch.float32 and t["il"].grad.dtype == torch.float32
+    a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
+    yo = oracle.oracle_fwd(*a, h0=q["h0"] if state else None)
+    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(yo, dt)) < 2e-3
+    g = oracle.oracle_bwd(*a, q["dy"], h0=q["h0"] if state else None, dhT=d["dhT"] if state else None)
+    for k, src in GRADS:
+        got = t[src].grad.float().cpu().numpy()
+        if src in ("fl", "il"):
+            assert oracle.rel_l2(got, g[k]) < 2e-4, k
+        else:
+            ref = g[k] if k == "dD" else _round(g[k], dt)
+            assert oracle.rel_l2(got, ref) < TOL_GRAD, k
+
+
 def test_strided_bc_views_and_no_grad():
     """B and C arrive as two views of one [B,T,2N] tensor (naju/mixer.py:116)."""
     from naju_b200 import naju_scan
