@@ -151,9 +151,10 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t sbase = smem_u32(smem);
-  const int b = static_cast<int>(blockIdx.x) / p.ndt, dt = static_cast<int>(blockIdx.x) % p.ndt;
-  const int d0 = dt * kDT;
+  // channel tiles (one batch row x 128 channels) are dealt round-robin over the grid; `it` counts
+  // the (channel tile, chunk) pairs a CTA has seen and selects the barrier phases
   const int per_chunk = p.B * p.ndt;
+  const int x_first = static_cast<int>(blockIdx.x), x_step = static_cast<int>(gridDim.x);
   const int nchunks = p.nchunks;
 
   if (tid == 0) {
@@ -191,8 +192,11 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     // ===================================================================== TMA producer
     if (lane == 0) {
       uint32_t slab = 0;
-      for (int it = 0; it < nchunks; ++it) {
-        const int c = nchunks - 1 - it, t0 = c * Q, par = it & 1;
+      int it = 0;
+      for (int x = x_first; x < per_chunk; x += x_step) {
+      const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
+      for (int ci = 0; ci < nchunks; ++ci, ++it) {
+        const int c = nchunks - 1 - ci, t0 = c * Q, par = it & 1;
         if (it >= 2 && !mbar_wait(smem_u32(&bars.bc_empty[par]), ((it >> 1) & 1) ^ 1)) timeout();
         {
           const uint32_t bar = smem_u32(&bars.bc_full[par]);
@@ -213,6 +217,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           tma_load_3d(dst + Smem::off_sdy, &maps.dy, d0, t0 + k * SLAB, b, bar);
         }
       }
+      }
     }
   } else if (warp == 9) {
     // ===================================================================== operand builder
@@ -221,7 +226,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     unsigned char* s_BB = smem + Smem::off_BB;
     unsigned char* s_CT = smem + Smem::off_CT;
     unsigned char* s_BT = smem + Smem::off_BT;
-    for (int it = 0; it < nchunks; ++it) {
+    const int ntile = ((per_chunk - x_first + x_step - 1) / x_step) * nchunks;
+    for (int it = 0; it < ntile; ++it) {
       const int par = it & 1;
       if (!mbar_wait(smem_u32(&bars.bc_full[par]), (it >> 1) & 1)) timeout();
       // C | g1 | g2 and the B rows are read only by the previous tile's first MMA round: they can
@@ -300,7 +306,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       // accumulator row 64+s (the lane of the thread that holds V[s,:]); rows 0-63 are never read
       const uint64_t dMk = umma_desc(aM, 128, SBO_M), dMm = umma_desc(aM - 8 * 128, SBO_M, 128);
       auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
-      for (int it = 0; it < nchunks; ++it) {
+      const int ntile = ((per_chunk - x_first + x_step - 1) / x_step) * nchunks;
+      for (int it = 0; it < ntile; ++it) {
         const uint32_t par = it & 1;
         if (!mbar_wait(smem_u32(&bars.opsA_full), par)) timeout();
 #pragma unroll
@@ -388,23 +395,20 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     // 63-32 to get r_32.
     const int half = warp >> 2;
     const int cid = tid & (kDT - 1);  // channel within the tile
-    const int d = d0 + cid;
-    const bool d_ok = d < p.D;
-    const int cols = min(kDT, p.D - d0);
+    // coordinates of the channel tile in hand (set at the top of the channel-tile loop)
+    int b = 0, dt = 0, d0 = 0, d = 0, cols = 0, xt = 0;
+    bool d_ok = false;
+    float Dv = 0.f;
     const uint32_t trow = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     unsigned char* rows = smem + Smem::off_rows;
     unsigned char* my_row = rows + static_cast<uint32_t>(cid >> 3) * SBO_R + static_cast<uint32_t>(cid & 7) * 16;
-    const float Dv = d_ok ? __ldg(p.Dskip + d) : 0.f;
     float lam[NS];  // adjoint entering the current chunk from the future (kept by both halves)
-#pragma unroll
-    for (int n = 0; n < NS; ++n)
-      lam[n] = (p.dhT != nullptr && d_ok && n < p.N) ? p.dhT[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
     float dDsum = 0.f;
     uint32_t slab = 0;
     PROFB_INIT;
     // dC / dB partial rows of the previous tile, written one tile late
     float UV[NS];
-    int pend_t0 = 0, pend_len = 0;
+    int pend_t0 = 0, pend_len = 0, pend_b = 0, pend_dt = 0;
     uint32_t pend_par = 0;
     bool pending = false;
     auto flush_pending = [&]() {
@@ -419,7 +423,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         const int tt = cid & 63;
         if (tt < pend_len) {
           float* dst = (cid < 64 ? p.dCpart : p.dBpart) +
-                       ((static_cast<int64_t>(b) * p.T + pend_t0 + tt) * p.ndt + dt) * NS;
+                       ((static_cast<int64_t>(pend_b) * p.T + pend_t0 + tt) * p.ndt + pend_dt) * NS;
 #pragma unroll
           for (int q4 = 0; q4 < NS / 4; ++q4)
             reinterpret_cast<float4*>(dst)[q4] =
@@ -444,7 +448,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     // halves), hv = state entering it (first half only; h0 for the first chunk)
     float xe[NS], hv[NS];
     auto fetch_states = [&](int c) {
-      const int64_t tile = static_cast<int64_t>(c) * per_chunk + blockIdx.x;
+      const int64_t tile = static_cast<int64_t>(c) * per_chunk + xt;
       const float4* src = reinterpret_cast<const float4*>(p.ckS + (tile * kDT + cid) * NS);
 #pragma unroll
       for (int q4 = 0; q4 < NS / 4; ++q4) {
@@ -466,10 +470,24 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
       }
     };
+    int it = 0;
+    for (int x = x_first; x < per_chunk; x += x_step) {
+    xt = x;
+    b = x / p.ndt;
+    dt = x - b * p.ndt;
+    d0 = dt * kDT;
+    d = d0 + cid;
+    d_ok = d < p.D;
+    cols = min(kDT, p.D - d0);
+    Dv = d_ok ? __ldg(p.Dskip + d) : 0.f;
+#pragma unroll
+    for (int n = 0; n < NS; ++n)
+      lam[n] = (p.dhT != nullptr && d_ok && n < p.N) ? p.dhT[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
+    dDsum = 0.f;
     fetch_states(nchunks - 1);
 
-    for (int it = 0; it < nchunks; ++it) {
-      const int c = nchunks - 1 - it, t0 = c * Q, len = min(Q, p.T - t0);
+    for (int ci = 0; ci < nchunks; ++ci, ++it) {
+      const int c = nchunks - 1 - ci, t0 = c * Q, len = min(Q, p.T - t0);
       const uint32_t par = it & 1;
       // xe / hv (state at the chunk end / entering the chunk) were fetched during the previous
       // tile; the first half posts the h rows right away
@@ -778,13 +796,14 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       pend_t0 = t0;
       pend_len = len;
       pend_par = par;
+      pend_b = b;
+      pend_dt = dt;
       pending = true;
       tc_fence_before();
       mbar_arrive(smem_u32(&bars.tile_done));
       bar_sync<1, NMAIN>();  // rows, output staging and TMEM are free for the next tile
       PROFB_MARK(8);
     }
-    flush_pending();
     // channel tile done: D_skip partials (one row per half and batch row), gradient of h0
     p.dDpart[(static_cast<int64_t>(half) * p.B + b) * (p.ndt * kDT) + d0 + cid] = dDsum;
     if (half == 0 && p.dh0 != nullptr && d_ok) {
@@ -793,6 +812,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       for (int n = 0; n < NS; ++n)
         if (n < p.N) o[n] = lam[n];
     }
+    }
+    flush_pending();
   }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
@@ -876,7 +897,8 @@ int launch_bwd_tc_t(const BwdParams& p, const tcb::Maps& maps, const int* fwd_fo
   constexpr size_t smem = tcb::SmemT<TG>::total;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<static_cast<unsigned>(ctiles), tcb::NTHREADS, smem, st>>>(p, maps, fwd_form);
+  const int64_t grid = std::min<int64_t>(ctiles, sm_count_b());
+  kern<<<static_cast<unsigned>(grid), tcb::NTHREADS, smem, st>>>(p, maps, fwd_form);
   return static_cast<int>(cudaGetLastError());
 }
 }  // namespace
@@ -887,7 +909,9 @@ int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int 
         bc == NAJU_BF16))
     return -1000;
   const int64_t ctiles = static_cast<int64_t>(g.B) * g.ndt;
-  if (!(ctiles * 2 >= sm_count_b() && ctiles <= sm_count_b() && g.nchunks >= 4)) return -1000;
+  // One persistent CTA per SM walks whole channel tiles: with fewer than about a third of the SMs
+  // busy the exact recurrent backward (which spreads over time as well) is the faster one.
+  if (!(ctiles * 3 >= sm_count_b() && g.nchunks >= 4)) return -1000;
   tcb::Maps maps;
   const bool ok =
       make_map_b(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB) &&

@@ -231,9 +231,8 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
   tc_fence_after();
   const uint32_t tmem = s_tmem;
   auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
-  if constexpr (WALK) {
-    if (blockIdx.x == 0 && tid == 0) atomicOr(p.fwd_form, 1);  // tell the backward how the forward ran
-  }
+  // tell the backward that the chunked forward ran (it has watched every tile for deep gates)
+  if (blockIdx.x == 0 && tid == 0) atomicOr(p.fwd_form, 1);
 
   if (warp == 8) {
     // ===================================================================== TMA producer
@@ -754,11 +753,9 @@ int launch_tc2_m(const FwdParams& p, const Geometry& g, const tc2::Maps& maps, c
 
 template <typename TA, typename TG>
 int launch_tc2_t(const FwdParams& p, const Geometry& g, const tc2::Maps& maps, cudaStream_t st) {
-  // Walking each channel tile along time keeps the carry on chip, but needs enough channel tiles
-  // to occupy the SMs (all of them resident at once: at most one CTA per SM fits).
-  const int64_t ctiles = static_cast<int64_t>(g.B) * g.ndt;
-  const bool walk = ctiles * 2 >= sm_count() && ctiles <= sm_count() && g.nchunks >= 4;
-  return walk ? launch_tc2_m<TA, TG, true>(p, g, maps, st) : launch_tc2_m<TA, TG, false>(p, g, maps, st);
+  // Problems with enough channel tiles to walk them along time are taken by the newer kernel
+  // (fwd_tc3.cu) before this one is asked; what arrives here spreads over time by ticket.
+  return launch_tc2_m<TA, TG, false>(p, g, maps, st);
 }
 
 }  // namespace
