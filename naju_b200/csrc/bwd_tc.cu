@@ -137,7 +137,10 @@ struct Bars {
   unsigned long long d1_full, d4_full, m2_full, d5_full, tile_done;
 };
 
-template <typename TA, typename TG>
+// MULTI: a CTA may be dealt more than one channel tile (grid = number of SMs); without it the grid is
+// the number of channel tiles and the outer loops below run exactly once, which the compiler
+// knows (the single-tile kernel needs a few registers less and does not spill).
+template <typename TA, typename TG, bool MULTI>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* __restrict__ fwd_form) {
   using Smem = SmemT<TG>;
@@ -193,7 +196,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     if (lane == 0) {
       uint32_t slab = 0;
       int it = 0;
-      for (int x = x_first; x < per_chunk; x += x_step) {
+      int x = x_first;
+      do {
       const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
       for (int ci = 0; ci < nchunks; ++ci, ++it) {
         const int c = nchunks - 1 - ci, t0 = c * Q, par = it & 1;
@@ -217,7 +221,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           tma_load_3d(dst + Smem::off_sdy, &maps.dy, d0, t0 + k * SLAB, b, bar);
         }
       }
-      }
+      x += x_step;
+      } while (MULTI && x < per_chunk);
     }
   } else if (warp == 9) {
     // ===================================================================== operand builder
@@ -226,7 +231,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     unsigned char* s_BB = smem + Smem::off_BB;
     unsigned char* s_CT = smem + Smem::off_CT;
     unsigned char* s_BT = smem + Smem::off_BT;
-    const int ntile = ((per_chunk - x_first + x_step - 1) / x_step) * nchunks;
+    const int ntile = MULTI ? ((per_chunk - x_first + x_step - 1) / x_step) * nchunks : nchunks;
     for (int it = 0; it < ntile; ++it) {
       const int par = it & 1;
       if (!mbar_wait(smem_u32(&bars.bc_full[par]), (it >> 1) & 1)) timeout();
@@ -306,7 +311,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       // accumulator row 64+s (the lane of the thread that holds V[s,:]); rows 0-63 are never read
       const uint64_t dMk = umma_desc(aM, 128, SBO_M), dMm = umma_desc(aM - 8 * 128, SBO_M, 128);
       auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
-      const int ntile = ((per_chunk - x_first + x_step - 1) / x_step) * nchunks;
+      const int ntile = MULTI ? ((per_chunk - x_first + x_step - 1) / x_step) * nchunks : nchunks;
       for (int it = 0; it < ntile; ++it) {
         const uint32_t par = it & 1;
         if (!mbar_wait(smem_u32(&bars.opsA_full), par)) timeout();
@@ -395,10 +400,6 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     // 63-32 to get r_32.
     const int half = warp >> 2;
     const int cid = tid & (kDT - 1);  // channel within the tile
-    // coordinates of the channel tile in hand (set at the top of the channel-tile loop)
-    int b = 0, dt = 0, d0 = 0, d = 0, cols = 0, xt = 0;
-    bool d_ok = false;
-    float Dv = 0.f;
     const uint32_t trow = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     unsigned char* rows = smem + Smem::off_rows;
     unsigned char* my_row = rows + static_cast<uint32_t>(cid >> 3) * SBO_R + static_cast<uint32_t>(cid & 7) * 16;
@@ -444,9 +445,17 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       *reinterpret_cast<uint4*>(my_row + (c_lo + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
     };
 
+    float xe[NS], hv[NS];
+    int it = 0;
+    int x = x_first;
+    do {
+    // coordinates of the channel tile in hand
+    const int xt = x, b = x / p.ndt, dt = x - b * p.ndt, d0 = dt * kDT, d = d0 + cid;
+    const bool d_ok = d < p.D;
+    const int cols = min(kDT, p.D - d0);
+    const float Dv = d_ok ? __ldg(p.Dskip + d) : 0.f;
     // checkpointed states of a chunk: xe = state at its end (seed of the r recurrence, both
     // halves), hv = state entering it (first half only; h0 for the first chunk)
-    float xe[NS], hv[NS];
     auto fetch_states = [&](int c) {
       const int64_t tile = static_cast<int64_t>(c) * per_chunk + xt;
       const float4* src = reinterpret_cast<const float4*>(p.ckS + (tile * kDT + cid) * NS);
@@ -470,16 +479,6 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
       }
     };
-    int it = 0;
-    for (int x = x_first; x < per_chunk; x += x_step) {
-    xt = x;
-    b = x / p.ndt;
-    dt = x - b * p.ndt;
-    d0 = dt * kDT;
-    d = d0 + cid;
-    d_ok = d < p.D;
-    cols = min(kDT, p.D - d0);
-    Dv = d_ok ? __ldg(p.Dskip + d) : 0.f;
 #pragma unroll
     for (int n = 0; n < NS; ++n)
       lam[n] = (p.dhT != nullptr && d_ok && n < p.N) ? p.dhT[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
@@ -812,7 +811,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       for (int n = 0; n < NS; ++n)
         if (n < p.N) o[n] = lam[n];
     }
-    }
+    x += x_step;
+    } while (MULTI && x < per_chunk);
     flush_pending();
   }
   __syncthreads();
@@ -893,8 +893,9 @@ int sm_count_b() {
 namespace {
 template <typename TA, typename TG>
 int launch_bwd_tc_t(const BwdParams& p, const tcb::Maps& maps, const int* fwd_form, int64_t ctiles, cudaStream_t st) {
-  auto kern = tcb::bwd_tc_kernel<TA, TG>;
   constexpr size_t smem = tcb::SmemT<TG>::total;
+  const bool multi = ctiles > sm_count_b();
+  auto kern = multi ? tcb::bwd_tc_kernel<TA, TG, true> : tcb::bwd_tc_kernel<TA, TG, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   const int64_t grid = std::min<int64_t>(ctiles, sm_count_b());
