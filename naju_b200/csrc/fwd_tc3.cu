@@ -45,7 +45,10 @@ namespace tc3 {
 using namespace tcx;
 
 constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, RING = 4, NSTAGE = 2;
-constexpr int NHALF = 128, NGATE = 256, NEPI = 256, NTHREADS = 608;
+// NGRP gate groups of 128 threads: group g owns the steps of slabs [g * NSLAB / NGRP, (g + 1) * NSLAB / NGRP)
+constexpr int NGRP = 2, SPG = NSLAB / NGRP;  // (four groups measured slower: the gate warps already fill the issue slots)
+constexpr int NHALF = 128, NGATE = NGRP * 128, NEPI = 256, NTHREADS = NEPI + NGATE + 96;
+constexpr int W_PROD = (NEPI + NGATE) / 32, W_BUILD = W_PROD + 1, W_MMA = W_PROD + 2;
 constexpr int AW_W1 = 0, AW_W2 = 8;
 constexpr uint32_t SBO_AW = 16 * 128, AW_BYTES = 16 * SBO_AW;  // operand rows [w1 64 | w2 64], per stage
 constexpr int AH_H1 = 0, AH_H2 = 2;
@@ -210,7 +213,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
   const uint32_t tmem = s_tmem;
   auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
 
-  if (warp == 16) {
+  if (warp == W_PROD) {
     // ===================================================================== TMA producer
     if (lane == 0) {
       uint32_t slab = 0;
@@ -258,7 +261,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       }
       if (it >= 1) load_u_copy(it - 1);
     }
-  } else if (warp == 17) {
+  } else if (warp == W_BUILD) {
     // ===================================================================== operand builder
     const int g = lane >> 2, t4 = lane & 3;
     int it = 0;
@@ -318,7 +321,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         }
       }
     }
-  } else if (warp == 18) {
+  } else if (warp == W_MMA) {
     // ===================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t id16 = umma_idesc(128, NS, 1), id64 = umma_idesc(128, Q, 1);
@@ -368,7 +371,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     }
   } else if (warp >= 8) {
     // ===================================================================== gate warps
-    const int half = (warp - 8) >> 2;      // 0: steps 0-31 of each chunk, 1: steps 32-63
+    const int half = (warp - 8) >> 2;      // gate group: which slabs of every chunk this thread evaluates
     const int q = tid & (kDT - 1);         // channel within the tile
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t slab = 0;
@@ -389,7 +392,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
 #pragma unroll 1
         for (int k = 0; k < NSLAB; ++k) {
           const uint32_t sidx = slab + k, slot = sidx % RING, ph = (sidx / RING) & 1;
-          const bool mine = (k >> 1) == half;
+          const bool mine = (k / SPG) == half;
           // (every thread waits for the slab before releasing it, needed or not: an arrival must
           // not reach the empty barrier before its previous phase has completed)
 #ifdef NAJU_PROF
@@ -404,8 +407,8 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           const TG* s_fl = reinterpret_cast<const TG*>(sl + SLAB * kDT * 2) + q;
           const TG* s_il = s_fl + SLAB * kDT;
           if (!mine) {
-            if (half == 1) {
-              // second thread on slabs 0,1: retention products only.  The sixteen factors are
+            if (k / SPG < half) {
+              // slabs before this group's: retention products only.  The sixteen factors are
               // independent: multiply them as a tree, not as a chain.
               float fac[SLAB];
 #pragma unroll
@@ -455,7 +458,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         slab += NSLAB;
         PROF_MARK(16 + 8 * half + 1);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        const bool deep = half == 1 && !(R < kRMax);  // the second thread holds the whole chunk's product
+        const bool deep = half == NGRP - 1 && !(R < kRMax);  // the last group holds the whole chunk's product
         const bool any_deep = bar_or<2, NGATE>(deep);
         if (tid == 8 * 32) s_stage_deep[st] = any_deep ? 1 : 0;
         tc_fence_before();
