@@ -319,6 +319,71 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """Decode-step leg (not the headline): one token for 24 layers of state [256, 2048, 16] fp32,
+    each layer's state updated in place by one launch.  24 x 33.5 MB of state (805 MB) is larger
+    than L2, so every launch reads and writes its state from HBM: 2*N*4 bytes per channel plus the
+    token's u / logits / y."""
+    import torch
+    from naju_b200 import naju_scan_step
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback for the scan)")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    L, Bsz, D, N = 24, 256, 2048, 16
+    g = torch.Generator(device=dev).manual_seed(3)
+    states = [torch.randn(Bsz, D, N, device=dev, generator=g) for _ in range(L)]
+    bf = torch.bfloat16
+    u = torch.randn(Bsz, D, device=dev, generator=g).to(bf)
+    fl = (torch.randn(Bsz, D, device=dev, generator=g) + 2).to(bf)
+    il = torch.randn(Bsz, D, device=dev, generator=g).to(bf)
+    Bm = (torch.randn(Bsz, N, device=dev, generator=g) / 4).to(bf)
+    Cm = (torch.randn(Bsz, N, device=dev, generator=g) / 4).to(bf)
+    Dk = torch.zeros(D, device=dev)
+
+    def step():
+        for st in states:
+            naju_scan_step(st, u, fl, il, Bm, Cm, Dk)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    eager_ms = timed(step)
+    # the 24 launches of one token captured once in a CUDA graph and replayed (no per-launch host work)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    ms = timed(graph.replay)
+    nbytes = L * (2 * Bsz * D * N * 4 + Bsz * D * 2 * 4)
+    peak, peak_kind = measured_peak()
+    gbs = nbytes / (ms / 1e3) / 1e9
+    print(json.dumps({
+        "metric": "decode state update, 24 layers x batch 256 x D=2048 x N=16", "value": Bsz / (ms / 1e3),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "decode: 24 launches of step_kernel per token (one CUDA graph replay), state in place",
+                   "eager_ms_per_step": eager_ms},
+        "roofline": {"bound": "hbm", "kernel": "step_kernel", "achieved": gbs, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "algorithmic_bytes_per_launch": nbytes // L},
+        "gpu_launches": L * args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -328,12 +393,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--shape", default=None, help="B,T,D,N instead of the metric workload (profiling)")
+    ap.add_argument("--workload", default="train", choices=["train", "decode"],
+                    help="train = the headline fwd+bwd scan; decode = the single-token state update")
     args = ap.parse_args()
     args.shape = tuple(int(x) for x in args.shape.split(",")) if args.shape else \
         (CFG["B"], CFG["T"], CFG["D"], CFG["N"])
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_gpu_arm(args)
 
