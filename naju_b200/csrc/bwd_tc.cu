@@ -51,7 +51,7 @@ constexpr uint32_t SBO_BB = 2 * 128, BB_BYTES = 8 * SBO_BB;      // rows s: [B 2
 constexpr uint32_t SBO_T = 8 * 128, T_BYTES = 2 * SBO_T;         // rows n: [X^T 8]      2048 (CT and BT)
 // M2 operand rows t: [m1 8 | m2 8]; 64 real rows, addressed as 128 (the rest is never used)
 constexpr int M_1 = 0, M_2 = 8;
-constexpr uint32_t SBO_M = 16 * 128, M_BYTES = 8 * SBO_M;        // 16384
+constexpr uint32_t SBO_M = 16 * 128;                         // 8 row groups = 16384 bytes
 constexpr uint32_t BC_BYTES = Q * NS * 2;
 // TMEM columns
 constexpr uint32_t TM_Y = 0, TM_G = 64, TM_DL = 128, TM_X = 144, TM_DCI = 240, TM_CF = 256, TM_CI = 320,
@@ -96,7 +96,7 @@ __device__ unsigned long long g_profb[16];
 #endif
 
 struct Maps {
-  CUtensorMap u, fl, il, dy, bm, cm;
+  CUtensorMap u, fl, il, dy, bm, cm, du, dfl, dil;
 };
 
 // TG = type of the logits and of their gradients.  With 16-bit logits all three output tiles are
@@ -585,6 +585,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         for (int n = 0; n < NS; ++n) lt[n] = PQ * lam[n];
         write_split_rows(lt, R_L1, R_L2);
       }
+      if (tid == 0) tma_store_wait_read();  // the previous tile's output tiles have left the staging area
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(smem_u32(&bars.carry_full));
@@ -731,25 +732,25 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 #undef NAJU_TWAIT16
 #undef NAJU_TWAIT8
       PROFB_MARK(6);
+      fence_async_smem();
       tc_fence_before();
       bar_sync<1, NMAIN>();
-      {  // du, d f_logit, d i_logit tiles out with 16-byte stores
-        const int64_t goff = (static_cast<int64_t>(b) * p.T + t0) * p.D + d0;
-        TA* gout[3] = {reinterpret_cast<TA*>(p.du) + goff, reinterpret_cast<TA*>(p.dfl) + goff,
-                       reinterpret_cast<TA*>(p.dil) + goff};
-#pragma unroll
-        for (int w3 = 0; w3 < (Smem::kStageGates ? 3 : 1); ++w3) {
-          const unsigned char* src = out_u + w3 * (Q * kDT * 2);
-#pragma unroll
-          for (int i = 0; i < (Q * kDT * 2 / 16) / NMAIN; ++i) {
-            const int v16 = i * NMAIN + tid, t = v16 >> 4, c16 = v16 & 15;
-            if (t < len && c16 * 8 < cols)
-              *reinterpret_cast<uint4*>(gout[w3] + static_cast<int64_t>(t) * p.D + c16 * 8) =
-                  *reinterpret_cast<const uint4*>(src + (t * kDT + c16 * 8) * 2);
-          }
+      if (tid == 0) {
+        // du, d f_logit, d i_logit tiles out by TMA (steps past T and channels past D are clipped), one
+        // bulk group each; the M2 operand re-uses the du tile, so wait until the du group has been read
+        tma_store_3d(&maps.du, d0, t0, b, smem_u32(out_u));
+        tma_store_commit();
+        if constexpr (Smem::kStageGates) {
+          tma_store_3d(&maps.dfl, d0, t0, b, smem_u32(out_f));
+          tma_store_commit();
+          tma_store_3d(&maps.dil, d0, t0, b, smem_u32(out_i));
+          tma_store_commit();
+          tma_store_wait_read_but<2>();
+        } else {
+          tma_store_wait_read();
         }
       }
-      bar_sync<1, NMAIN>();  // staging fully read before the M2 operand overwrites part of it
+      bar_sync<1, NMAIN>();  // the du tile has been read: the M2 operand may overwrite it
       PROFB_MARK(7);
 
       // ---------------- cross-channel block (its MMAs ran during the sweep): lanes t < 64 hold row t
@@ -814,6 +815,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     x += x_step;
     } while (MULTI && x < per_chunk);
     flush_pending();
+    if (tid == 0) tma_store_wait_all();
   }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
@@ -913,14 +915,20 @@ int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int 
   // One persistent CTA per SM walks whole channel tiles: with fewer than about a third of the SMs
   // busy the exact recurrent backward (which spreads over time as well) is the faster one.
   if (!(ctiles * 3 >= sm_count_b() && g.nchunks >= 4)) return -1000;
-  tcb::Maps maps;
+  tcb::Maps maps = {};
   const bool ok =
       make_map_b(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB) &&
       make_map_b(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tcb::SLAB) &&
       make_map_b(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tcb::SLAB) &&
       make_map_b(&maps.dy, p.dy, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::SLAB) &&
       make_map_b(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tcb::NS, tcb::Q) &&
-      make_map_b(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q);
+      make_map_b(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q) &&
+      // outputs are dense [B, T, D]; one 64-step x 128-channel box per store (fp32 logit gradients
+      // are written from registers, not by TMA)
+      make_map_b(&maps.du, p.du, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q) &&
+      (gate == NAJU_F32 ||
+       (make_map_b(&maps.dfl, p.dfl, gate, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q) &&
+        make_map_b(&maps.dil, p.dil, gate, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q)));
   if (!ok) return -1000;
   if (gate == NAJU_F32)
     return launch_bwd_tc_t<__nv_bfloat16, float>(p, maps, fwd_form, ctiles, static_cast<cudaStream_t>(stream));

@@ -176,6 +176,11 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all earlier store groups of this thread have finished READING shared memory (the tile may be reused)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the newest N store groups of this thread have finished reading shared memory
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read_but() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 // all earlier store groups of this thread are complete (before the kernel exits)
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
