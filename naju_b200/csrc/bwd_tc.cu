@@ -134,7 +134,7 @@ struct Bars {
   unsigned long long carry_full;   // h and lt rows written
   unsigned long long opsA_full;    // C | g1 | g2 and B rows built (first MMA round, contraction over time/state)
   unsigned long long opsB_full;    // C^T and B^T built (dL and the second MMA round)
-  unsigned long long d1_full, d4_full, m2_full, d5_full, tile_done;
+  unsigned long long d1_full, d4_full, m2_full, d5_full;
 };
 
 // MULTI: a CTA may be dealt more than one channel tile (grid = number of SMs); without it the grid is
@@ -177,7 +177,6 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     mbar_init(smem_u32(&bars.d4_full), 1);
     mbar_init(smem_u32(&bars.m2_full), NMAIN);
     mbar_init(smem_u32(&bars.d5_full), 1);
-    mbar_init(smem_u32(&bars.tile_done), NMAIN);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
@@ -332,25 +331,33 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g1, iKK64, ks > 0);
           umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g2, iKK64, 1u);
           umma_bf16(tmem + TM_Y, dRk + off((R_W2 + 2 * ks) * 128), g1, iKK64, 1u);
+          if (ks == 0) {
+            // Yt += (h1 + h2).C   (K = n): the h rows were written by the threads of slab 0 before
+            // they released it, so this part of the carry does not have to wait for the carry barrier
+            umma_bf16(tmem + TM_Y, dRk + off(R_H1 * 128), dGk + off(BG_C * 128), iKK64, 1u);
+            umma_bf16(tmem + TM_Y, dRk + off(R_H2 * 128), dGk + off(BG_C * 128), iKK64, 1u);
+          }
           // gt += al1.g1^T + al1.g2^T + al2.g1^T   (K = t: the G buffer read MN-major)
           const uint64_t g1t = dGm + off(2 * ks * SBO_BG + BG_G1 * 128), g2t = dGm + off(2 * ks * SBO_BG + BG_G2 * 128);
           umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g1t, iKM64, ks > 0);
           umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g2t, iKM64, 1u);
           umma_bf16(tmem + TM_G, dRk + off((R_A2 + 2 * ks) * 128), g1t, iKM64, 1u);
+          // dL += al1.C + al2.C   (K = t, B operand = C^T rows), slab by slab as well; C^T comes a
+          // little later than the other shared operands, so the first slab's share waits for ks = 1
+          if (ks == 1) {
+            if (!mbar_wait(smem_u32(&bars.opsB_full), par)) timeout();
+            tc_fence_after();
+            umma_bf16(tmem + TM_DL, dRk + off(R_A1 * 128), dCT, iKK16, 0u);
+            umma_bf16(tmem + TM_DL, dRk + off(R_A2 * 128), dCT, iKK16, 1u);
+          }
+          if (ks >= 1) {
+            umma_bf16(tmem + TM_DL, dRk + off((R_A1 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, 1u);
+            umma_bf16(tmem + TM_DL, dRk + off((R_A2 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, 1u);
+          }
         }
-        // dL += al1.C + al2.C   (K = t, B operand = C^T rows)
-        if (!mbar_wait(smem_u32(&bars.opsB_full), par)) timeout();
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          umma_bf16(tmem + TM_DL, dRk + off((R_A1 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, ks > 0);
-          umma_bf16(tmem + TM_DL, dRk + off((R_A2 + 2 * ks) * 128), dCT + off(2 * ks * 128), iKK16, 1u);
-        }
-        // Yt += (h1 + h2).C,  gt += (l1 + l2).B   (K = n)
+        // gt += (l1 + l2).B   (K = n): the only MMAs that need the whole chunk's retention product
         if (!mbar_wait(smem_u32(&bars.carry_full), par)) timeout();
         tc_fence_after();
-        umma_bf16(tmem + TM_Y, dRk + off(R_H1 * 128), dGk + off(BG_C * 128), iKK64, 1u);
-        umma_bf16(tmem + TM_Y, dRk + off(R_H2 * 128), dGk + off(BG_C * 128), iKK64, 1u);
         umma_bf16(tmem + TM_G, dRk + off(R_L1 * 128), dBB, iKK64, 1u);
         umma_bf16(tmem + TM_G, dRk + off(R_L2 * 128), dBB, iKK64, 1u);
         umma_commit(smem_u32(&bars.d1_full));  // the reverse sweep can start
@@ -800,8 +807,9 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       pend_dt = dt;
       pending = true;
       tc_fence_before();
-      mbar_arrive(smem_u32(&bars.tile_done));
-      bar_sync<1, NMAIN>();  // rows, output staging and TMEM are free for the next tile
+      // (the hazards of the next tile are all ordered by MMA barriers already; this barrier keeps
+      // the eight warps in step, which measured 7 % faster than letting them drift)
+      bar_sync<1, NMAIN>();
       PROFB_MARK(8);
     }
     // channel tile done: D_skip partials (one row per half and batch row), gradient of h0
