@@ -150,12 +150,12 @@ def run_reference_arm(args):
 
 def ncu_traffic_bwd(B, T, D, N):
     """DRAM bytes of one tensor-core backward launch, from the ncu capture summarised in
-    profiles/tensor_core_kernels_B8_T2048_D2048_N16.md: 496.3 MB for 16384 tokens at D=2048, N=16
+    profiles/tensor_core_kernels_B8_T2048_D2048_N16.md: 497 MB for 16384 tokens at D=2048, N=16
     (dram__bytes.sum.per_second x gpu__time_duration).  Traffic grows in proportion to the tokens
     (every tile moves the same bytes), so a full launch is that figure scaled by the token count."""
     if (D, N) != (2048, 16):
         return None
-    return 496.3e6 / 16384.0 * (B * T)
+    return 497.0e6 / 16384.0 * (B * T)
 
 
 # ----------------------------------------------------------------------------- GPU arm

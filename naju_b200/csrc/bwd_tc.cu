@@ -100,7 +100,7 @@ struct Maps {
 };
 
 // TG = type of the logits and of their gradients.  With 16-bit logits all three output tiles are
-// staged in shared memory and written with 16-byte stores; with fp32 logits the input slabs are
+// staged in shared memory and written by TMA stores; with fp32 logits the input slabs are
 // larger, only du is staged, and d f_logit / d i_logit go out straight from registers (a warp's
 // 32 consecutive fp32 values are a full 128-byte line).
 template <typename TG>
