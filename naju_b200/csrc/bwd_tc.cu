@@ -313,7 +313,13 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       const int ntile = MULTI ? ((per_chunk - x_first + x_step - 1) / x_step) * nchunks : nchunks;
       for (int it = 0; it < ntile; ++it) {
         const uint32_t par = it & 1;
+#ifdef NAJU_PROF
+        const long long t_oa = clock64();
+#endif
         if (!mbar_wait(smem_u32(&bars.opsA_full), par)) timeout();
+#ifdef NAJU_PROF
+        atomicAdd(&g_profb[14], static_cast<unsigned long long>(clock64() - t_oa));
+#endif
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           // the MMAs that contract over time need only the row chunks of slab ks: they run while
@@ -345,7 +351,13 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           // dL += al1.C + al2.C   (K = t, B operand = C^T rows), slab by slab as well; C^T comes a
           // little later than the other shared operands, so the first slab's share waits for ks = 1
           if (ks == 1) {
+#ifdef NAJU_PROF
+            const long long t_ob = clock64();
+#endif
             if (!mbar_wait(smem_u32(&bars.opsB_full), par)) timeout();
+#ifdef NAJU_PROF
+            atomicAdd(&g_profb[15], static_cast<unsigned long long>(clock64() - t_ob));
+#endif
             tc_fence_after();
             umma_bf16(tmem + TM_DL, dRk + off(R_A1 * 128), dCT, iKK16, 0u);
             umma_bf16(tmem + TM_DL, dRk + off(R_A2 * 128), dCT, iKK16, 1u);
