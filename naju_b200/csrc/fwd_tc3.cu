@@ -14,16 +14,17 @@
 // bits; the dropped w2.g2 term is 2^-16 relative), so the tensor-core path keeps ~1e-5 accuracy.
 //
 // One persistent CTA per SM walks channel tiles (one batch row x 128 channels) along time, so
-// the carry never leaves the chip.  Nineteen warps in five roles, two pipeline stages (operand
+// the carry never leaves the chip.  Twenty warps in five roles, two pipeline stages (operand
 // rows, shared operands and TMEM accumulators are double buffered):
 //   warp 16     TMA producer: u / f_logit / i_logit in 16-step slabs through a 4-deep mbarrier
-//               ring, plus the chunk's B and C rows.
+//               ring, plus the chunk's B and C rows and a second copy of u for the epilogue.
 //   warps 8-15  gate warps, two threads per channel (steps 0-31 / 32-63 of the chunk; the second
 //               thread first multiplies up the retention of steps 0-31 to enter step 32 with
 //               the right product): sigmoids, running products, the channel's operand row
 //               (K-major, no swizzle) and P_t, which goes to TMEM with tcgen05.st.
-//   warp 17     operand builder: C | g1 | g2 and B^T of the tile with mma.sync.
-//   warp 18     MMA issuer: one thread issues every tcgen05.mma, slab by slab as the gate warps
+//   warps 17-18 operand builders: C | g1 | g2 and B^T of the tile with mma.sync (16x8 blocks of G dealt
+//               round-robin), started as soon as the MMAs of the tile two back have read the stage.
+//   warp 19     MMA issuer: one thread issues every tcgen05.mma, slab by slab as the gate warps
 //               deliver, and every tcgen05.commit.
 //   warps 0-7   carry/epilogue warps: warps 0-3 turn D2 into the next chunk's carry-in (registers),
 //               write the checkpoint and post the carry-in row one tile ahead; all eight read
@@ -46,9 +47,12 @@ using namespace tcx;
 
 constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, RING = 4, NSTAGE = 2;
 // NGRP gate groups of 128 threads: group g owns the steps of slabs [g * NSLAB / NGRP, (g + 1) * NSLAB / NGRP)
-constexpr int NGRP = 2, SPG = NSLAB / NGRP;  // (four groups measured slower: the gate warps already fill the issue slots)
-constexpr int NHALF = 128, NGATE = NGRP * 128, NEPI = 256, NTHREADS = NEPI + NGATE + 96;
-constexpr int W_PROD = (NEPI + NGATE) / 32, W_BUILD = W_PROD + 1, W_MMA = W_PROD + 2;
+constexpr int NGRP = 2, SPG = NSLAB / NGRP;  // (four groups measured slower: 0.89 ms against 0.83 ms)
+// NBUILD operand-builder warps share a tile's work (one warp alone takes 5.5 k cycles per tile, longer
+// than the gate warps; with two the MMA issuer no longer waits for operands; four measured slower)
+constexpr int NBUILD = 2;
+constexpr int NHALF = 128, NGATE = NGRP * 128, NEPI = 256, NTHREADS = NEPI + NGATE + 32 * (2 + NBUILD);
+constexpr int W_PROD = (NEPI + NGATE) / 32, W_BUILD = W_PROD + 1, W_MMA = W_BUILD + NBUILD;
 constexpr int AW_W1 = 0, AW_W2 = 8;
 constexpr uint32_t SBO_AW = 16 * 128, AW_BYTES = 16 * SBO_AW;  // operand rows [w1 64 | w2 64], per stage
 constexpr int AH_H1 = 0, AH_H2 = 2;
@@ -84,7 +88,17 @@ __device__ unsigned long long g_prof[48];
     }                                                                     \
   } while (0)
 #define PROF_INIT long long pt_ = clock64()
+// same for the single-warp roles (lane 0 marks)
+#define PROF_MARK1(i)                                                     \
+  do {                                                                    \
+    if ((threadIdx.x & 31) == 0) {                                        \
+      const long long now_ = clock64();                                   \
+      atomicAdd(&g_prof[i], static_cast<unsigned long long>(now_ - pt_)); \
+      pt_ = now_;                                                         \
+    }                                                                     \
+  } while (0)
 #else
+#define PROF_MARK1(i) do {} while (0)
 #define PROF_MARK(i) do {} while (0)
 #define PROF_INIT do {} while (0)
 #endif
@@ -118,7 +132,7 @@ struct Bars {
   unsigned long long ops_full[NSTAGE];          // builder -> MMA issuer
   unsigned long long d2_full[NSTAGE];           // D2 and the first part of D1 complete
   unsigned long long h_ready;                   // carry warps -> MMA issuer (carry-in row written)
-  unsigned long long d1_full;                   // D1 complete
+  unsigned long long d1_full[NSTAGE];           // D1 complete (and the stage's shared operands read)
   unsigned long long stage_free[NSTAGE];        // carry/epilogue warps -> everyone upstream
 };
 
@@ -187,18 +201,18 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.bc_full[i]), 1);
-      mbar_init(smem_u32(&bars.bc_empty[i]), 1);
+      mbar_init(smem_u32(&bars.bc_empty[i]), NBUILD);
     }
     for (int i = 0; i < NSTAGE; ++i) {
       for (int k = 0; k < NSLAB; ++k) mbar_init(smem_u32(&bars.part[i][k]), NHALF);
       mbar_init(smem_u32(&bars.a_full[i]), NGATE);
       mbar_init(smem_u32(&bars.u_full[i]), 1);
-      mbar_init(smem_u32(&bars.ops_full[i]), 1);
+      mbar_init(smem_u32(&bars.ops_full[i]), NBUILD);
       mbar_init(smem_u32(&bars.d2_full[i]), 1);
       mbar_init(smem_u32(&bars.stage_free[i]), NEPI);
     }
     mbar_init(smem_u32(&bars.h_ready), NHALF);
-    mbar_init(smem_u32(&bars.d1_full), 1);
+    for (int i = 0; i < NSTAGE; ++i) mbar_init(smem_u32(&bars.d1_full[i]), 1);
     mbar_init_fence();
     if (blockIdx.x == 0) atomicOr(p.fwd_form, 1);  // tell the backward how the forward ran
   }
@@ -261,26 +275,29 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       }
       if (it >= 1) load_u_copy(it - 1);
     }
-  } else if (warp == W_BUILD) {
-    // ===================================================================== operand builder
+  } else if (warp >= W_BUILD && warp < W_BUILD + NBUILD) {
+    // ===================================================================== operand builders
     const int g = lane >> 2, t4 = lane & 3;
+    const int bw = warp - W_BUILD, blane = bw * 32 + lane;
     int it = 0;
+    PROF_INIT;
     for (int x = x_first; x < ctiles; x += x_step) {
       for (int c = 0; c < nchunks; ++c, ++it) {
         const int st = it & 1;
         if (!mbar_wait(smem_u32(&bars.bc_full[st]), (it >> 1) & 1)) timeout();
-        // stage st: the tile two back must be completely done with B1 / B2
-        if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.stage_free[st]), ((it >> 1) & 1) ^ 1)) timeout();
+        // stage st: the MMAs of the tile two back must have read B1 / B2 (its epilogue may still run)
+        if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.d1_full[st]), ((it >> 1) & 1) ^ 1)) timeout();
+        PROF_MARK1(40);
         unsigned char* s_B1 = smem + SM::off_B1 + st * B1_BYTES;
         unsigned char* s_B2 = smem + SM::off_B2 + st * B2_BYTES;
         const __nv_bfloat16* Braw = reinterpret_cast<const __nv_bfloat16*>(smem + SM::off_bc + st * 2 * BC_BYTES);
         const __nv_bfloat16* Craw = Braw + Q * NS;
-        for (int e = lane; e < Q * 2; e += 32) {  // C columns of B1: 32 bytes per row
+        for (int e = blane; e < Q * 2; e += 32 * NBUILD) {  // C columns of B1: 32 bytes per row
           const int t = e >> 1, half = e & 1;
           *reinterpret_cast<uint4*>(s_B1 + op_off16(t, B1_C * 8 + half * 8, SBO_B1)) =
               *reinterpret_cast<const uint4*>(Craw + t * NS + half * 8);
         }
-        for (int e = lane; e < NS * (Q / 8); e += 32) {  // B2 = B^T: (row n, eight columns s) per store
+        for (int e = blane; e < NS * (Q / 8); e += 32 * NBUILD) {  // B2 = B^T: (row n, eight columns s) per store
           const int n = e % NS, s8 = e / NS;
           uint32_t w[4];
 #pragma unroll
@@ -299,6 +316,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           const uint32_t a2 = *reinterpret_cast<const uint32_t*>(Craw + r0 * NS + 2 * t4 + 8);
           const uint32_t a3 = *reinterpret_cast<const uint32_t*>(Craw + r1 * NS + 2 * t4 + 8);
           for (int nt = 0; nt <= 2 * mt + 1; ++nt) {
+            if (((mt * (mt + 1) + nt) % NBUILD) != bw) continue;  // 16x8 blocks dealt round-robin to the builder warps
             float c4[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Braw + (8 * nt + g) * NS + 2 * t4);
             const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Braw + (8 * nt + g) * NS + 2 * t4 + 8);
@@ -319,6 +337,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           mbar_arrive(smem_u32(&bars.ops_full[st]));
           mbar_arrive(smem_u32(&bars.bc_empty[st]));
         }
+        PROF_MARK1(41);
       }
     }
   } else if (warp == W_MMA) {
@@ -338,7 +357,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           const uint64_t dAW = dAW0 + off(st * AW_BYTES), dB1 = dB10 + off(st * B1_BYTES), dB2 = dB20 + off(st * B2_BYTES);
           const uint32_t tst = tmem + st * TM_STAGE;
           if (!mbar_wait(smem_u32(&bars.ops_full[st]), par)) timeout();
-          PROF_MARK(32);
+          PROF_MARK1(32);
 #pragma unroll 1
           for (int ks = 0; ks < NSLAB; ++ks) {
             // the time contractions of slab ks run while the gate warps are still on the other slabs
@@ -353,19 +372,19 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
           // a deep-gate tile is decided only now (all gate threads done): its accumulators are junk
           // and are simply not read; one carry-in phase per tile keeps the phase counts aligned
-          PROF_MARK(33);
+          PROF_MARK1(33);
           if (!mbar_wait(smem_u32(&bars.a_full[st]), par)) timeout();
           umma_commit(smem_u32(&bars.d2_full[st]));
-          PROF_MARK(34);
+          PROF_MARK1(34);
           if (!mbar_wait(smem_u32(&bars.h_ready), it & 1)) timeout();
-          PROF_MARK(35);
+          PROF_MARK1(35);
           if (!s_stage_deep[st]) {
             tc_fence_after();
             umma_bf16(tst + TM_D1, dAH + off(AH_H1 * 128), dB1 + off(B1_C * 128), id64, 1u);  // D1 += (h1 + h2) . C
             umma_bf16(tst + TM_D1, dAH + off(AH_H2 * 128), dB1 + off(B1_C * 128), id64, 1u);
           }
-          umma_commit(smem_u32(&bars.d1_full));
-          PROF_MARK(36);
+          umma_commit(smem_u32(&bars.d1_full[st]));
+          PROF_MARK1(36);
         }
       }
     }
@@ -550,7 +569,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
         }
         PROF_MARK(8 * half + 1);
-        if (!mbar_wait(smem_u32(&bars.d1_full), it & 1)) timeout();
+        if (!mbar_wait(smem_u32(&bars.d1_full[st]), (it >> 1) & 1)) timeout();
         PROF_MARK(8 * half + 2);
         tc_fence_after();
         if (half == 0) {
