@@ -64,6 +64,9 @@ constexpr uint32_t BC_BYTES = Q * NS * 2;
 constexpr uint32_t TM_D1 = 0, TM_D2 = 64, TM_P = 96, TM_STAGE = 160, TMEM_COLS = 512;
 constexpr float kRMax = 1.0e24f;  // ~2^80
 constexpr float kNegLog2e = -1.4426950408889634f;
+// nanoseconds between polls for the roles that have slack (producer, builders, the epilogue warps'
+// first wait of a tile); the gate warps and the MMA issuer poll without sleeping
+constexpr int kRelaxProd = 100, kRelaxBuild = 100, kRelaxEpi = 64;
 constexpr int EPI_A_COLS = 16;    // columns of a tile the carry warps take in the epilogue (rest: warps 4-7)
 
 __device__ __forceinline__ float fast_ex2(float x) {
@@ -238,7 +241,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       auto load_u_copy = [&](int j) {
         if constexpr (SM::kStashU) {
           const int st = j & 1;
-          if (j >= NSTAGE && !mbar_wait(smem_u32(&bars.stage_free[st]), ((j >> 1) & 1) ^ 1)) timeout();
+          if (j >= NSTAGE && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.stage_free[st]), ((j >> 1) & 1) ^ 1)) timeout();
           const uint32_t bar = smem_u32(&bars.u_full[st]);
           mbar_arrive_expect_tx(bar, Q * kDT * 2);
           for (int k = 0; k < NSLAB; ++k)
@@ -253,7 +256,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           pb = b;
           pd0 = d0;
           pt0 = t0;
-          if (it >= 2 && !mbar_wait(smem_u32(&bars.bc_empty[it & 1]), ((it >> 1) & 1) ^ 1)) timeout();
+          if (it >= 2 && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.bc_empty[it & 1]), ((it >> 1) & 1) ^ 1)) timeout();
           {
             const uint32_t bar = smem_u32(&bars.bc_full[it & 1]);
             const uint32_t dst = sbase + SM::off_bc + (it & 1) * 2 * BC_BYTES;
@@ -263,7 +266,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
           for (int k = 0; k < NSLAB; ++k, ++slab) {
             const uint32_t slot = slab % RING, ph = (slab / RING) & 1;
-            if (slab >= RING && !mbar_wait(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
+            if (slab >= RING && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
             const uint32_t bar = smem_u32(&bars.full[slot]);
             const uint32_t dst = sbase + SM::off_ring + slot * SM::slab_bytes;
             mbar_arrive_expect_tx(bar, SM::slab_bytes);
@@ -284,9 +287,9 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     for (int x = x_first; x < ctiles; x += x_step) {
       for (int c = 0; c < nchunks; ++c, ++it) {
         const int st = it & 1;
-        if (!mbar_wait(smem_u32(&bars.bc_full[st]), (it >> 1) & 1)) timeout();
+        if (!mbar_wait_relaxed<kRelaxBuild>(smem_u32(&bars.bc_full[st]), (it >> 1) & 1)) timeout();
         // stage st: the MMAs of the tile two back must have read B1 / B2 (its epilogue may still run)
-        if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.d1_full[st]), ((it >> 1) & 1) ^ 1)) timeout();
+        if (it >= NSTAGE && !mbar_wait_relaxed<kRelaxBuild>(smem_u32(&bars.d1_full[st]), ((it >> 1) & 1) ^ 1)) timeout();
         PROF_MARK1(40);
         unsigned char* s_B1 = smem + SM::off_B1 + st * B1_BYTES;
         unsigned char* s_B2 = smem + SM::off_B2 + st * B2_BYTES;
@@ -533,7 +536,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       const float Dv = tcd.d_ok ? __ldg(p.Dskip + tcd.d) : 0.f;
       for (int c = 0; c < nchunks; ++c, ++it) {
         const int st = it & 1;
-        if (!mbar_wait(smem_u32(&bars.d2_full[st]), (it >> 1) & 1)) timeout();
+        if (!mbar_wait_relaxed<kRelaxEpi>(smem_u32(&bars.d2_full[st]), (it >> 1) & 1)) timeout();
         PROF_MARK(8 * half);
         tcd.c = c;
         tcd.tile = static_cast<int64_t>(c) * ctiles + x;

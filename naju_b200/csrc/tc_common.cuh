@@ -154,6 +154,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same wait for warps with slack (they are waiting most of the time, and a tight polling loop
+// takes issue slots from the working warps of their scheduler): sleep NS nanoseconds between
+// tries.  Bounded like mbar_wait.
+template <int NS>
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t mbar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n"
+      "NAJU_MBAR_RTRY:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "@p bra NAJU_MBAR_RDONE;\n\t"
+      "nanosleep.u32 %5;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 q, n, %4;\n\t"
+      "@q bra NAJU_MBAR_RTRY;\n"
+      "NAJU_MBAR_RDONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(mbar), "r"(parity), "r"(4096u), "r"(1u << 22), "n"(NS)
+      : "memory");
+  return ok != 0;
+}
+
 // ---- TMA: 3-D tiled load global -> shared, completion counted on an mbarrier.  Plain
 // (non-multicast) form only.  The innermost coordinate times the element size must be a
 // multiple of 16 bytes.
