@@ -221,6 +221,41 @@ def test_tensor_core_fp32_logits(case):
             assert oracle.rel_l2(got, ref) < TOL_GRAD, k
 
 
+@pytest.mark.parametrize("gate32", [False, True])
+def test_tensor_core_forward_fp16(gate32):
+    """fp16 activations (with fp16 or fp32 logits) at a shape the walk-along-time tensor-core forward
+    takes; B and C stay bf16 (the tensor-core operand type).  The backward of this mix is the
+    recurrent one.  Compared with the fp64 oracle on the same quantised inputs."""
+    from naju_b200 import naju_scan
+    B, T, D, N = 4, 300, 2432, 16
+    dt = torch.float16
+    d = oracle.make_inputs(B, T, D, N, seed=7, f_shift=2.0, d_skip_scale=0.01, with_h0=True)
+    q = dict(d)
+    for k in ("u", "dy") + (() if gate32 else ("fl", "il")):
+        q[k] = _round(d[k], dt)
+    for k in ("Bm", "Cm"):
+        q[k] = _round(d[k], torch.bfloat16)
+    t = {"u": torch.tensor(q["u"], device="cuda").to(dt),
+         "fl": torch.tensor(q["fl"], device="cuda").to(torch.float32 if gate32 else dt),
+         "il": torch.tensor(q["il"], device="cuda").to(torch.float32 if gate32 else dt),
+         "Bm": torch.tensor(q["Bm"], device="cuda").to(torch.bfloat16),
+         "Cm": torch.tensor(q["Cm"], device="cuda").to(torch.bfloat16),
+         "Dskip": torch.tensor(q["Dskip"], device="cuda"), "h0": torch.tensor(q["h0"], device="cuda")}
+    for v in t.values():
+        v.requires_grad_(True)
+    y, hT = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"], h0=t["h0"], return_final_state=True)
+    torch.autograd.backward([y, hT], [torch.tensor(q["dy"], device="cuda").to(dt), torch.tensor(d["dhT"], device="cuda")])
+    torch.cuda.synchronize()
+    a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
+    yo, hTo = oracle.oracle_fwd(*a, h0=q["h0"], return_final_state=True)
+    assert oracle.rel_l2(hT.detach().cpu().numpy(), hTo) < TOL_FWD
+    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(yo, dt)) < TOL_FWD
+    g = oracle.oracle_bwd(*a, q["dy"], h0=q["h0"], dhT=d["dhT"])
+    assert oracle.rel_l2(t["u"].grad.float().cpu().numpy(), _round(g["du"], dt)) < TOL_GRAD
+    assert oracle.rel_l2(t["fl"].grad.float().cpu().numpy(), g["dfl"] if gate32 else _round(g["dfl"], dt)) < TOL_GRAD
+    assert oracle.rel_l2(t["Bm"].grad.float().cpu().numpy(), _round(g["dB"], torch.bfloat16)) < TOL_GRAD
+
+
 def test_strided_bc_views_and_no_grad():
     """B and C arrive as two views of one [B,T,2N] tensor (naju/mixer.py:116)."""
     from naju_b200 import naju_scan
