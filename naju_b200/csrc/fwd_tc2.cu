@@ -114,10 +114,9 @@ struct Bars {
   unsigned long long stage_free[NSTAGE];        // carry/epilogue warps -> everyone upstream
 };
 
-// Exact two-pass recurrence of one tile straight from global memory (deep-gate tiles only).
-// WALK: the carry-in arrives in hw[] / Pw (state and cumulative decay entering the chunk) and
-// the chunk-end values are returned there; otherwise the carry goes through the look-back.
-template <typename TA, typename TG, bool WALK>
+// Exact two-pass recurrence of one tile straight from global memory (deep-gate tiles only); the
+// carry goes through the look-back (hw / Pw are scratch).
+template <typename TA, typename TG>
 __device__ __noinline__ void exact_tile_from_global(const FwdParams& p, const TileCoord& tc, int tid,
                                                     float (&hw)[NS], float& Pw) {
   const TA* gu = reinterpret_cast<const TA*>(p.u) + tc.b * p.u_sb + static_cast<int64_t>(tc.t0) * p.u_st + tc.d;
@@ -127,11 +126,7 @@ __device__ __noinline__ void exact_tile_from_global(const FwdParams& p, const Ti
   const int64_t cbase = tc.b * p.cm_sb + static_cast<int64_t>(tc.t0) * p.cm_st;
   float x[NS], h[NS];
   float P = 1.f, Pin;
-  if constexpr (WALK) {
-    Pin = Pw;
-#pragma unroll
-    for (int n = 0; n < NS; ++n) h[n] = hw[n];
-  } else {
+  {
 #pragma unroll
     for (int n = 0; n < NS; ++n) x[n] = 0.f;
     for (int t = 0; t < tc.len; ++t) {
@@ -168,27 +163,14 @@ __device__ __noinline__ void exact_tile_from_global(const FwdParams& p, const Ti
     }
     if (tc.d_ok) gy[static_cast<int64_t>(t) * p.D] = from_f32<TA>(fmaf(Dv, ut, acc));
   }
-  if constexpr (WALK) {
-    // chunk-end state and cumulative decay: the next chunk's carry-in and the checkpoint
-    const int64_t slot = tc.tile * kDT + tid;
-    float4* dstS = reinterpret_cast<float4*>(p.ckS + slot * NS);
-#pragma unroll
-    for (int q = 0; q < NS / 4; ++q) dstS[q] = make_float4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
-    Pw = Pin * Pc;
-    p.ckP[slot] = Pw;
-#pragma unroll
-    for (int n = 0; n < NS; ++n) hw[n] = h[n];
-    write_final<NS>(p, tc, h, Pw);
-  } else {
+  {
     write_final<NS>(p, tc, h, P * Pin);
   }
 }
 
-// WALK = true : CTA x owns channel tile x (one batch row, 128 channels) and walks its chunks in
-//               time order; the carry stays in the registers of the carry warps (grid = B * ndt).
-// WALK = false: tiles come from the time-major ticket and the carry crosses CTAs by look-back
-//               (for problems with too few channel tiles to fill the GPU).
-template <typename TA, typename TG, bool WALK>
+// Tiles come from the time-major ticket and the carry crosses CTAs by look-back: the form for
+// problems with too few channel tiles to fill the GPU by walking them along time (fwd_tc3.cu).
+template <typename TA, typename TG>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int ntiles) {
   using SM = Smem<TG>;
@@ -240,9 +222,7 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
     for (int it = 0;; ++it) {
       int tile = 0;
       if (lane == 0) {
-        if constexpr (WALK) {
-          tile = it < p.nchunks ? it * (p.B * p.ndt) + static_cast<int>(blockIdx.x) : -1;
-        } else {
+        {
           const unsigned ticket = atomicAdd(&p.hdr->ticket, 1u);
           tile = ticket < static_cast<unsigned>(ntiles) ? static_cast<int>(ticket) : -1;
         }
@@ -518,18 +498,9 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
       mbar_arrive(smem_u32(&bars.h_ready));
     };
     uint32_t dph = 0;  // parity of the next d1_full phase (normal tiles only)
-    // WALK: state / cumulative decay entering the current chunk, carried in registers
-    float hc[NS];
+    float hc[NS];  // scratch for the exact path
     float Pc = 1.f;
-    // Exactly one carry-in row (one h_ready phase) is posted per tile, deep tiles included; in
-    // WALK mode the row of tile c+1 is posted while tile c is being finished.
-    if constexpr (WALK) {
-      const int b = static_cast<int>(blockIdx.x) / p.ndt, d = (static_cast<int>(blockIdx.x) % p.ndt) * kDT + tid;
-#pragma unroll
-      for (int n = 0; n < NS; ++n)
-        hc[n] = (p.h0 != nullptr && d < p.D && n < p.N) ? p.h0[(static_cast<int64_t>(b) * p.D + d) * p.N + n] : 0.f;
-      write_h_row(hc);
-    }
+    // Exactly one carry-in row (one h_ready phase) is posted per tile, deep tiles included.
     PROF_INIT;
     for (int it = 0;; ++it) {
       const int st = it & 1;
@@ -542,10 +513,8 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
       const int len = tcd.len;
       if (s_stage_deep[st]) {
         if (tid == 0) atomicOr(p.fwd_form, 2);
-        exact_tile_from_global<TA, TG, WALK>(p, tcd, tid, hc, Pc);
-        if constexpr (WALK) {
-          if (it + 1 < p.nchunks) write_h_row(hc);
-        } else {
+        exact_tile_from_global<TA, TG>(p, tcd, tid, hc, Pc);
+        {
           mbar_arrive(smem_u32(&bars.h_ready));  // keep the phase count: one per tile
         }
         mbar_arrive(smem_u32(&bars.stage_free[st]));
@@ -568,19 +537,7 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
         for (int n = 0; n < NS; ++n) S[n] = __uint_as_float(sr[n]) * P;
       }
       PROF_MARK(1);
-      if constexpr (WALK) {
-        // chunk-end state = next carry-in; it is also the backward's checkpoint
-        const int64_t slot = tcd.tile * kDT + tid;
-        float4* dstS = reinterpret_cast<float4*>(p.ckS + slot * NS);
-#pragma unroll
-        for (int n = 0; n < NS; ++n) hc[n] = fmaf(P, hc[n], S[n]);
-#pragma unroll
-        for (int q4 = 0; q4 < NS / 4; ++q4)
-          dstS[q4] = make_float4(hc[4 * q4], hc[4 * q4 + 1], hc[4 * q4 + 2], hc[4 * q4 + 3]);
-        Pc *= P;
-        p.ckP[slot] = Pc;
-        write_final<NS>(p, tcd, hc, Pc);
-      } else {
+      {
         float h[NS], Pin;
         carry_lookback<NS, true>(p, tcd, tid, S, P, h, Pin);
         write_h_row(h);
@@ -594,11 +551,7 @@ fwd_tc2_kernel(const FwdParams p, const __grid_constant__ Maps maps, const int n
       dph ^= 1;
       tc_fence_after();
       PROF_MARK(3);
-      if constexpr (WALK) {
-        // the last MMA of this tile has read the carry-in row: post the next tile's row now, so
-        // that its last MMA never waits for these warps
-        if (it + 1 < p.nchunks) write_h_row(hc);
-      }
+      
       PROF_MARK(4);
 
       // ---- epilogue: y_t = P_t D1[d][t] + D_skip u_t, staged in the (now dead) w1 columns of
@@ -739,14 +692,14 @@ int sm_count() {
   return n;
 }
 
-template <typename TA, typename TG, bool WALK>
+template <typename TA, typename TG>
 int launch_tc2_m(const FwdParams& p, const Geometry& g, const tc2::Maps& maps, cudaStream_t st) {
   const size_t smem = tc2::Smem<TG>::total;
-  auto kern = tc2::fwd_tc2_kernel<TA, TG, WALK>;
+  auto kern = tc2::fwd_tc2_kernel<TA, TG>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   // one persistent CTA per SM; in walk mode one CTA per channel tile
-  const int64_t grid = WALK ? static_cast<int64_t>(g.B) * g.ndt : std::min<int64_t>(g.ntiles, sm_count());
+  const int64_t grid = std::min<int64_t>(g.ntiles, sm_count());
   kern<<<static_cast<unsigned>(grid), tc2::NTHREADS, smem, st>>>(p, maps, static_cast<int>(g.ntiles));
   return static_cast<int>(cudaGetLastError());
 }
@@ -755,7 +708,7 @@ template <typename TA, typename TG>
 int launch_tc2_t(const FwdParams& p, const Geometry& g, const tc2::Maps& maps, cudaStream_t st) {
   // Problems with enough channel tiles to walk them along time are taken by the newer kernel
   // (fwd_tc3.cu) before this one is asked; what arrives here spreads over time by ticket.
-  return launch_tc2_m<TA, TG, false>(p, g, maps, st);
+  return launch_tc2_m<TA, TG>(p, g, maps, st);
 }
 
 }  // namespace
