@@ -56,10 +56,6 @@ constexpr uint32_t BC_BYTES = Q * NS * 2;
 // TMEM columns
 constexpr uint32_t TM_Y = 0, TM_G = 64, TM_DL = 128, TM_X = 144, TM_DCI = 240, TM_CF = 256, TM_CI = 320,
                    TM_CU = 384, TM_DBI = 448, TMEM_COLS = 512;
-// The reverse sweep is split unevenly: the first-half threads also pre-sum the r-increments of the
-// other half's steps (a cheaper pass), so they take SWEEP_LO of the eight 8-step rounds and the
-// second-half threads the other 8 - SWEEP_LO; both then finish together.
-constexpr int SWEEP_LO = 3;
 constexpr float kRMax = 1.0e24f;
 constexpr float kNegLog2e = -1.4426950408889634f;
 
@@ -662,15 +658,15 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       // TMEM loads are software-pipelined in both loops: the next round's columns are in flight
       // while the current round is processed.
       if (half == 0) {
-        // first half: r-increments of the steps above its own only, to enter its top step with the right r
+        // first half: r-increments of steps 63..32 only, to enter step 31 with r_32
         uint32_t yq[2][8], gq[2][8];
         NAJU_TLD8(TM_Y, yq[1], Q / 8 - 1);
         NAJU_TLD8(TM_G, gq[1], Q / 8 - 1);
         NAJU_TWAIT16(yq[1], gq[1]);
 #pragma unroll
-        for (int ch = Q / 8 - 1; ch >= SWEEP_LO; --ch) {
+        for (int ch = Q / 8 - 1; ch >= Q / 16; --ch) {
           const int cur = ch & 1, nxt = cur ^ 1;
-          if (ch > SWEEP_LO) {
+          if (ch > Q / 16) {
             NAJU_TLD8(TM_Y, yq[nxt], ch - 1);
             NAJU_TLD8(TM_G, gq[nxt], ch - 1);
           }
@@ -687,12 +683,11 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
             const float wt = (j & 1) ? bf16hi_f32(pw1) + bf16hi_f32(pw2) : bf16lo_f32(pw1) + bf16lo_f32(pw2);
             rr += fmaf(al, __uint_as_float(yq[cur][j]), -wt * __uint_as_float(gq[cur][j]));
           }
-          if (ch > SWEEP_LO) NAJU_TWAIT16(yq[nxt], gq[nxt]);
+          if (ch > Q / 16) NAJU_TWAIT16(yq[nxt], gq[nxt]);
         }
       }
       {
-        const int ch_hi = half ? Q / 8 - 1 : SWEEP_LO - 1;
-        const int nrd = half ? Q / 8 - SWEEP_LO : SWEEP_LO;  // (warp-uniform)
+        const int ch_hi = half ? Q / 8 - 1 : Q / 16 - 1;
         uint32_t tq[2][5][8];
 #define NAJU_TLOAD_ROUND(BUF, CH)          \
   do {                                     \
@@ -711,11 +706,10 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         NAJU_TLOAD_ROUND(0, ch_hi);
         NAJU_TWAIT_ROUND(0);
 #pragma unroll
-        for (int rd = 0; rd < (SWEEP_LO > Q / 8 - SWEEP_LO ? SWEEP_LO : Q / 8 - SWEEP_LO); ++rd) {
-          if (rd >= nrd) break;
+        for (int rd = 0; rd < Q / 16; ++rd) {
           const int ch = ch_hi - rd;
           const int cur = rd & 1, nxt = cur ^ 1;
-          if (rd + 1 < nrd) NAJU_TLOAD_ROUND(nxt, ch - 1);
+          if (rd + 1 < Q / 16) NAJU_TLOAD_ROUND(nxt, ch - 1);
           const uint32_t* y8 = tq[cur][0];
           const uint32_t* g8 = tq[cur][1];
           const uint32_t* f8 = tq[cur][2];
@@ -748,7 +742,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
               gdil[static_cast<int64_t>(t) * p.D] = from_f32<TG>(dil);
             }
           }
-          if (rd + 1 < nrd) NAJU_TWAIT_ROUND(nxt);
+          if (rd + 1 < Q / 16) NAJU_TWAIT_ROUND(nxt);
         }
 #undef NAJU_TLOAD_ROUND
 #undef NAJU_TWAIT_ROUND
