@@ -27,15 +27,21 @@ def _pinned_like(shape, dtype):
     return torch.empty(shape, dtype=dtype).pin_memory()
 
 
-def scan_fwd_bwd_host(u, f_logit, i_logit, B, C, D_skip, dy, *, rows_per_chunk=1, device=None, out=None):
+def scan_fwd_bwd_host(u, f_logit, i_logit, B, C, D_skip, dy, *, rows_per_chunk=1, time_splits=1, device=None,
+                      out=None):
     """Forward and backward of the scan for host tensors.
 
     u, f_logit, i_logit, dy: [B, T, D]; B, C: [B, T, N] (pinned host memory for the copies to be
     asynchronous); D_skip: [D], host or device.  Returns a dict of host tensors
     {y, du, dfl, dil, dB, dC, dD}: y and du in u's dtype, the logit gradients in the logits' dtype,
     dB/dC in B's dtype, dD fp32.  `out` may hand in such a dict (pinned) to be filled again.
-    The call returns when all copies have been enqueued; the current stream then waits for them,
-    so a synchronize of the current stream (or device) makes the host tensors valid.
+    With time_splits = K > 1 (and rows_per_chunk = 1) every row is further cut into K contiguous
+    time segments: the forward runs segment by segment with the final state of one as the initial
+    state of the next, the backward runs them in reverse with the adjoint of the initial state
+    handed back the same way (the composition law of naju/tests/test_affine_chunk.py:47-78), and
+    copies move at segment granularity, which shortens the unoverlapped head and tail of the
+    pipeline.  The call returns when all copies have been enqueued; the current stream then waits
+    for them, so a synchronize of the current stream (or device) makes the host tensors valid.
     Same semantics as naju_scan (naju/scan.py:75-93) + autograd; zero initial state.
     """
     if not torch.cuda.is_available():
@@ -73,30 +79,61 @@ def scan_fwd_bwd_host(u, f_logit, i_logit, B, C, D_skip, dy, *, rows_per_chunk=1
                 slots.append([torch.empty((rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in ins])
         ev_in = [torch.cuda.Event() for _ in range(nchunk)]
         ev_cmp = [torch.cuda.Event() for _ in range(nchunk)]
+        K = max(1, int(time_splits)) if rows == 1 else 1
+        K = min(K, max(1, T // 256))  # segments shorter than a few chunks only add launches
+        seg = [(k * T // K, (k + 1) * T // K) for k in range(K)]
+        names = ("y", "du", "dfl", "dil", "dB", "dC")
+
+        def to_host(name, t, r0, r1, t0, t1):
+            dst = out[name][r0:r1, t0:t1]
+            dst.copy_(t.to(dst.dtype) if t.dtype != dst.dtype else t, non_blocking=True)
+            t.record_stream(s_out)
+
         for j in range(nchunk):
             r0, r1 = j * rows, min((j + 1) * rows, nb)
             n = r1 - r0
             slot = slots[j % len(slots)]
+            ev_seg = [torch.cuda.Event() for _ in range(K)]
             with torch.cuda.stream(s_in):
                 if j >= len(slots):
                     s_in.wait_event(ev_cmp[j - len(slots)])  # the kernels have read this slot's inputs
-                for dst, src in zip(slot, ins):
-                    dst[:n].copy_(src[r0:r1], non_blocking=True)
+                for k, (t0, t1) in enumerate(seg):
+                    for dst, src in zip(slot, ins):
+                        dst[:n, t0:t1].copy_(src[r0:r1, t0:t1], non_blocking=True)
+                    ev_seg[k].record(s_in)
                 ev_in[j].record(s_in)
+            fwd = []
+            ev_f = [torch.cuda.Event() for _ in range(K)]
+            ev_b = [torch.cuda.Event() for _ in range(K)]
+            grads = [None] * K
             with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in[j])
-                du_, fl_, il_, b_, c_, dy_ = (t[:n] for t in slot)
-                pu, pf, pi, pb, pc, pD = _prepare(du_, fl_, il_, b_, c_, Dk)
-                y, _, _, ckpt, desc = scan_forward(pu, pf, pi, pb, pc, pD)
-                g = scan_backward(desc, pu, pf, pi, pb, pc, pD, None, dy_, None, ckpt)
-                dD_acc += g[5]
+                h_prev = None
+                for k, (t0, t1) in enumerate(seg):
+                    s_cmp.wait_event(ev_seg[k])
+                    du_, fl_, il_, b_, c_, dy_ = (t[:n, t0:t1] for t in slot)
+                    pu, pf, pi, pb, pc, pD = _prepare(du_, fl_, il_, b_, c_, Dk)
+                    y, hT, _, ckpt, desc = scan_forward(pu, pf, pi, pb, pc, pD, h0=h_prev, want_final=K > 1)
+                    fwd.append((pu, pf, pi, pb, pc, pD, h_prev, dy_, ckpt, desc, y))
+                    h_prev = hT
+                    ev_f[k].record(s_cmp)
+                lam = None
+                for k in range(K - 1, -1, -1):
+                    pu, pf, pi, pb, pc, pD, h0k, dy_, ckpt, desc, _ = fwd[k]
+                    g = scan_backward(desc, pu, pf, pi, pb, pc, pD, h0k, dy_, lam, ckpt, want_dh0=k > 0)
+                    lam = g[6]
+                    dD_acc += g[5]
+                    grads[k] = g
+                    ev_b[k].record(s_cmp)
                 ev_cmp[j].record(s_cmp)
             with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[j])
-                for name, t in zip(("y", "du", "dfl", "dil", "dB", "dC"), (y,) + tuple(g[:5])):
-                    out[name][r0:r1].copy_(t.to(out[name].dtype) if t.dtype != out[name].dtype else t,
-                                           non_blocking=True)
-                    t.record_stream(s_out)
+                for k, (t0, t1) in enumerate(seg):
+                    s_out.wait_event(ev_f[k])
+                    to_host("y", fwd[k][10], r0, r1, t0, t1)
+                for k in range(K - 1, -1, -1):
+                    t0, t1 = seg[k]
+                    s_out.wait_event(ev_b[k])
+                    for name, t in zip(names[1:], grads[k][:5]):
+                        to_host(name, t, r0, r1, t0, t1)
         with torch.cuda.stream(s_out):
             s_out.wait_stream(s_cmp)
             out["dD"].copy_(dD_acc, non_blocking=True)

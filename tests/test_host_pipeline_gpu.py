@@ -13,19 +13,20 @@ def _round(a, dt):
     return torch.tensor(a).to(dt).float().numpy()
 
 
-@pytest.mark.parametrize("rows", [1, 2, 5])
-def test_host_pipeline_matches_oracle(rows):
-    """bf16 I/O, 5 batch rows in chunks of 1 / 2 (ragged last chunk) / all at once; outputs come
-    back in pinned host tensors.  Same tolerances as the device path (1e-3 forward, 2e-3
-    gradients against the identically rounded fp64 oracle)."""
+@pytest.mark.parametrize("rows,splits,T", [(1, 1, 200), (2, 1, 200), (5, 1, 200), (1, 3, 850), (1, 2, 600)])
+def test_host_pipeline_matches_oracle(rows, splits, T):
+    """bf16 I/O, 5 batch rows in chunks of 1 / 2 (ragged last chunk) / all at once, and rows cut
+    into 3 / 2 time segments chained through the final state and its adjoint; outputs come back
+    in pinned host tensors.  Same tolerances as the device path (1e-3 forward, 2e-3 gradients
+    against the identically rounded fp64 oracle)."""
     from naju_b200 import scan_fwd_bwd_host
-    B, T, D, N = 5, 200, 256, 16
+    B, D, N = 5, 256, 16
     dt = torch.bfloat16
     d = oracle.make_inputs(B, T, D, N, seed=11, d_skip_scale=0.05)
     q = {k: (_round(d[k], dt) if k in ("u", "fl", "il", "Bm", "Cm", "dy") else d[k]) for k in d}
     h = {k: torch.tensor(q[k]).to(dt).pin_memory() for k in ("u", "fl", "il", "Bm", "Cm", "dy")}
     out = scan_fwd_bwd_host(h["u"], h["fl"], h["il"], h["Bm"], h["Cm"], torch.tensor(q["Dskip"]), h["dy"],
-                            rows_per_chunk=rows)
+                            rows_per_chunk=rows, time_splits=splits)
     torch.cuda.synchronize()
     a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
     yo = oracle.oracle_fwd(*a)
