@@ -182,7 +182,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t mbar, uint32_t parity
 }
 
 // ---- TMA: 3-D tiled load global -> shared, completion counted on an mbarrier.  Plain
-// (non-multicast) form only.  The innermost coordinate times the element size must be a
+// (single-destination) form only.  The innermost coordinate times the element size must be a
 // multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1,
                                             int c2, uint32_t mbar) {
