@@ -12,8 +12,10 @@
 
 namespace naju {
 
+constexpr int kStepBlock = 128;  // (measured: 128 threads 20.2 us per launch, 256: 20.8, 512: 22.2)
+
 template <typename TA, typename TG>
-__global__ void __launch_bounds__(256) step_kernel(float* __restrict__ state, const TA* __restrict__ u,
+__global__ void __launch_bounds__(kStepBlock) step_kernel(float* __restrict__ state, const TA* __restrict__ u,
                                                    const TG* __restrict__ fl, const TG* __restrict__ il,
                                                    const void* __restrict__ Bm, const void* __restrict__ Cm,
                                                    const float* __restrict__ Dskip, TA* __restrict__ y,
@@ -36,12 +38,14 @@ __global__ void __launch_bounds__(256) step_kernel(float* __restrict__ state, co
     const int n0 = 4 * q;
     float* sp = state + chan * N + n0;
     if (n0 + 4 <= N && (N & 3) == 0) {
-      float4 s = *reinterpret_cast<float4*>(sp);
+      // the state is touched once per token: streaming (evict-first) accesses keep it from pushing
+      // the token's small inputs out of L2
+      float4 s = __ldcs(reinterpret_cast<const float4*>(sp));
       s.x = fmaf(f, s.x, w * load_dyn(Bm, bc_dtype, b * bm_sb + n0 + 0));
       s.y = fmaf(f, s.y, w * load_dyn(Bm, bc_dtype, b * bm_sb + n0 + 1));
       s.z = fmaf(f, s.z, w * load_dyn(Bm, bc_dtype, b * bm_sb + n0 + 2));
       s.w = fmaf(f, s.w, w * load_dyn(Bm, bc_dtype, b * bm_sb + n0 + 3));
-      *reinterpret_cast<float4*>(sp) = s;
+      __stcs(reinterpret_cast<float4*>(sp), s);
       part = s.x * load_dyn(Cm, bc_dtype, b * cm_sb + n0 + 0);
       part = fmaf(s.y, load_dyn(Cm, bc_dtype, b * cm_sb + n0 + 1), part);
       part = fmaf(s.z, load_dyn(Cm, bc_dtype, b * cm_sb + n0 + 2), part);
@@ -66,8 +70,8 @@ static int launch_t(const naju_scan_desc& d, float* state, const void* u, const 
   int lpc = 1;
   while (lpc * 4 < d.N) lpc <<= 1;  // 1..32
   const int64_t threads = static_cast<int64_t>(d.B) * d.D * lpc;
-  const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
-  step_kernel<TA, TG><<<blocks, 256, 0, st>>>(
+  const unsigned blocks = static_cast<unsigned>((threads + kStepBlock - 1) / kStepBlock);
+  step_kernel<TA, TG><<<blocks, kStepBlock, 0, st>>>(
       state, static_cast<const TA*>(u), static_cast<const TG*>(fl), static_cast<const TG*>(il), Bm,
       Cm, Dskip, static_cast<TA*>(y), d.B, d.D, d.N, lpc, d.bc_dtype, d.u_sb, d.fl_sb, d.il_sb,
       d.bm_sb, d.cm_sb);
