@@ -19,6 +19,8 @@
 #include "common.cuh"
 #include "params.h"
 
+#include <algorithm>
+
 namespace naju {
 
 constexpr int kG = 8;  // time steps between two cross-warp partial-sum flushes
@@ -43,15 +45,17 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
   if (p.tc_launched && (*p.fwd_form & 3) == 1) return;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // Persistent CTAs: each takes tile tickets (reverse-time-major, so the chunk a tile waits on is
+  // always held by a running CTA or done) until they run out.  The grid is a few CTAs per SM, which
+  // also makes the stand-down above cost a few microseconds instead of one CTA launch per tile.
+  for (;;) {
+  __syncthreads();  // the previous tile is done with shared memory (and with s_ticket)
   if (tid == 0) s_ticket = atomicAdd(&p.hdr->ticket, 1u);
   __syncthreads();
   const int per_chunk = p.B * p.ndt;
   const int order = static_cast<int>(s_ticket / per_chunk);  // 0 = last chunk in time
   const int rem = static_cast<int>(s_ticket % per_chunk);
-  if (order >= p.nchunks) {
-    if (tid == 0) atomicOr(&p.hdr->status, NAJU_ST_BAD_TILE);
-    return;
-  }
+  if (order >= p.nchunks) return;
   const int c = p.nchunks - 1 - order;
   const int b = rem / p.ndt, dt = rem % p.ndt;
   const int64_t tile = static_cast<int64_t>(c) * per_chunk + rem;
@@ -331,6 +335,7 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
   store_tile(reinterpret_cast<TA*>(p.du) + out_off, s_u, static_cast<int64_t>(p.D), len, cols, tid);
   store_tile(reinterpret_cast<TG*>(p.dfl) + out_off, s_fl, static_cast<int64_t>(p.D), len, cols, tid);
   store_tile(reinterpret_cast<TG*>(p.dil) + out_off, s_il, static_cast<int64_t>(p.D), len, cols, tid);
+  }
 }
 
 // out[row][n] = sum_k part[row][k][n] for n < N, written in the caller's dtype
@@ -376,7 +381,15 @@ static int launch_ns(const BwdParams& p, const Geometry& g, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<static_cast<unsigned>(g.ntiles), kThreads, smem, st>>>(p);
+  // persistent grid: what fits on the GPU at once (the look-back needs every waiting CTA's
+  // predecessors to be resident or done, which ticket order guarantees for any grid size)
+  int dev = 0, sms = 148, per_sm = 1;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const int64_t grid = std::min<int64_t>(g.ntiles, static_cast<int64_t>(sms) * per_sm);
+  kern<<<static_cast<unsigned>(grid), kThreads, smem, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
