@@ -757,7 +757,9 @@ int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act, int gate, int
   if (!(g.N == tc3::NS && g.TC == tc3::Q && act16 && bc == NAJU_BF16 && (gate == act || gate == NAJU_F32)))
     return -1000;
   if (g.ntiles >= (1LL << 31)) return -1000;
-  if (static_cast<int64_t>(g.B) * g.ndt * 2 < sm_count3() || g.nchunks < 4) return -1000;
+  // (with fewer than about a third of the SMs busy the ticket-mode kernel, which spreads over time as
+  // well, is the faster one)
+  if (static_cast<int64_t>(g.B) * g.ndt * 3 < sm_count3() || g.nchunks < 4) return -1000;
   tc3::Maps maps;
   const bool ok =
       make_map3(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tc3::SLAB) &&

@@ -155,7 +155,7 @@ def test_tensor_core_chunked_forward(monkeypatch, shape):
 @pytest.mark.parametrize("case", [(4, 256, 2432, 16, 2.0, True), (4, 520, 2432, 16, 2.0, False),
                                   (4, 520, 2432, 16, 4.0, True), (4, 520, 2432, 16, -2.5, True),
                                   # more channel tiles than SMs (some CTAs walk two of them), and
-                                  # only a third of the SMs busy (ticket-mode forward, walking backward)
+                                  # only a third of the SMs busy
                                   (2, 300, 12800, 16, 2.0, True), (1, 260, 6400, 16, 2.0, False)])
 def test_tensor_core_chunked_backward(case):
     """Forward and backward in the tcgen05 chunked form (the shapes have enough channel tiles for
