@@ -256,6 +256,28 @@ def test_tensor_core_forward_fp16(gate32):
     assert oracle.rel_l2(t["Bm"].grad.float().cpu().numpy(), _round(g["dB"], torch.bfloat16)) < TOL_GRAD
 
 
+def test_bf16_channel_count_tma_cannot_describe():
+    """D = 2434 is not a multiple of 8, so the bf16 row stride is not a multiple of 16 bytes and no
+    TMA descriptor exists for these tensors: the call must quietly take the kernels that do not
+    need one, with the same results."""
+    from naju_b200 import naju_scan
+    B, T, D, N = 4, 300, 2434, 16
+    dt = torch.bfloat16
+    d = oracle.make_inputs(B, T, D, N, seed=13, f_shift=2.0)
+    q = {k: (_round(d[k], dt) if k in ("u", "fl", "il", "Bm", "Cm", "dy") else d[k]) for k in d}
+    t = {k: torch.tensor(q[k], device="cuda").to(dt if k != "Dskip" else torch.float32).requires_grad_(True)
+         for k in ("u", "fl", "il", "Bm", "Cm", "Dskip")}
+    y = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"])
+    y.backward(torch.tensor(q["dy"], device="cuda").to(dt))
+    torch.cuda.synchronize()
+    a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
+    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(oracle.oracle_fwd(*a), dt)) < 2e-3
+    g = oracle.oracle_bwd(*a, q["dy"])
+    for k, src in GRADS:
+        ref = g[k] if k == "dD" else _round(g[k], dt)
+        assert oracle.rel_l2(t[src].grad.float().cpu().numpy(), ref) < TOL_GRAD, k
+
+
 def test_strided_bc_views_and_no_grad():
     """B and C arrive as two views of one [B,T,2N] tensor (naju/mixer.py:116)."""
     from naju_b200 import naju_scan
