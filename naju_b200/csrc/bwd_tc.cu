@@ -1,7 +1,7 @@
 // Backward gated scan, chunked (state-expansion) form on tcgen05 tensor cores.
 //
-// One persistent CTA per channel tile (one batch row x 128 channels) walks the chunks of Q = 64
-// steps in REVERSE time; the adjoint carry stays in registers, the state entering each chunk
+// A CTA owns channel tiles (one batch row x 128 channels; one per CTA, or dealt round-robin when
+// there are more tiles than SMs) and walks each one's chunks of Q = 64 steps in REVERSE time; the adjoint carry stays in registers, the state entering each chunk
 // comes from the checkpoints the forward saved.  Per chunk and channel d, with P_t = prod f,
 // R_t = 1/P_t, wt_s = w_s R_s (w = sigmoid(i_logit) u), al_t = dy_t P_t, h the state entering
 // the chunk, lam the adjoint entering it from the future, lt = P_Q lam and G = tril(C B^T):
@@ -22,9 +22,9 @@
 // state) and as MN-major operands for the cross-channel ones (contraction over the 128 channels),
 // and the G buffer serves K-major for Yt and MN-major (i.e. transposed) for gt.
 //
-// Warps: 0-3 thread = channel (gates -> operand rows and per-step coefficients into TMEM; after
-// the MMAs the reverse-time epilogue), 4 TMA producer, 5 shared-operand builder (mma.sync),
-// 6 MMA issuer.  Every wait is bounded.  Tiles with deep retention gates (prod f < 2^-80 in a
+// Warps: 0-7 main, two threads per channel (gates -> operand rows and per-step coefficients into
+// TMEM; after the MMAs the reverse-time sweep; the output tiles leave by TMA store), 8 TMA
+// producer, 9 shared-operand builder (mma.sync), 10 MMA issuer.  Every wait is bounded.  Tiles with deep retention gates (prod f < 2^-80 in a
 // chunk) cannot be factorised; the forward records whether it met one, and this kernel stands
 // down in that case (the exact recurrent backward runs instead).
 #include <algorithm>
