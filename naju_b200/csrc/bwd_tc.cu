@@ -1,8 +1,9 @@
 // Backward gated scan, chunked (state-expansion) form on tcgen05 tensor cores.
 //
 // A CTA owns channel tiles (one batch row x 128 channels; one per CTA, or dealt round-robin when
-// there are more tiles than SMs) and walks each one's chunks of Q = 64 steps in REVERSE time; the adjoint carry stays in registers, the state entering each chunk
-// comes from the checkpoints the forward saved.  Per chunk and channel d, with P_t = prod f,
+// there are more tiles than SMs) and walks each one's chunks of Q = 64 steps in REVERSE time; the
+// adjoint carry stays in registers, the state entering each chunk comes from the checkpoints the
+// forward saved.  Per chunk and channel d, with P_t = prod f,
 // R_t = 1/P_t, wt_s = w_s R_s (w = sigmoid(i_logit) u), al_t = dy_t P_t, h the state entering
 // the chunk, lam the adjoint entering it from the future, lt = P_Q lam and G = tril(C B^T):
 //
