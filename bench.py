@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE.json's metric): B=8, T=16384, D=2048, N=16, bf16 inputs, fp32 state,
+Workload (the headline metric's configuration): B=8, T=16384, D=2048, N=16, bf16 inputs, fp32 state,
 synthetic seeded inputs u~N(0,1), f_logit~N(2,1), i_logit~N(0,1), B,C~N(0,1/N), dy~N(0,1).
 A step is one forward + one backward scan over that batch.  With N>1 GPUs every rank runs
 the same batch shape on its own data (batch sharding, no collective): weak scaling.

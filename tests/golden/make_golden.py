@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 Every fixture is produced by naju.scan.naju_scan_reference (naju/scan.py:79-93) and
 torch autograd through it.  Inputs come from oracle.make_inputs (a seeded numpy
@@ -27,7 +27,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path of the reference checkout>")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 from naju.scan import naju_scan_reference  # noqa: E402  (the reference itself)
@@ -37,7 +39,7 @@ torch.set_num_threads(max(1, os.cpu_count() or 1))
 
 # name -> (kwargs of make_inputs, post-processing tag)
 CASES = {
-    # BASELINE config 0
+    # config 0 of the reference's benchmark list
     "cfg0_B2_T512_D64_N16": dict(B=2, T=512, D=64, N=16, seed=0, f_shift=2.0, i_shift=0.0),
     # reference GPU smoke distribution (naju/tests/test_gpu_smoke.py:32-45)
     "smoke_B2_T256_D64_N16": dict(B=2, T=256, D=64, N=16, seed=10, f_shift=3.0, i_shift=-2.0,
@@ -56,7 +58,7 @@ CASES = {
     # deep gates (naju/tests/test_affine_chunk.py:101-115: f_logit - 14)
     "deep_B2_T128_D64_N64": dict(B=2, T=128, D=64, N=64, seed=7, f_shift=-12.0, i_shift=-1.0,
                                  d_skip_scale=0.01),
-    # near-1 retention (BASELINE config 2 distribution, short)
+    # near-1 retention (the long-sequence config's distribution, short)
     "slow_B1_T300_D48_N16": dict(B=1, T=300, D=48, N=16, seed=2, f_shift=4.0, i_shift=0.0),
     # initial/final state extension, via neutral bracket steps
     "state_B2_T96_D32_N16": dict(B=2, T=96, D=32, N=16, seed=11, f_shift=2.0, i_shift=0.0,

@@ -1,4 +1,4 @@
-"""The BASELINE configs as GPU cases: the mixer-shaped call (config 1), the long near-1-retention
+"""The benchmark configurations as GPU cases: the mixer-shaped call (config 1), the long near-1-retention
 scan (config 2, reduced for the oracle; full size through size-independent properties), the
 decode stack (config 3, one layer's update at full batch) and the wide-state config 4 (reduced).
 """
@@ -101,7 +101,7 @@ def _metric_inputs(B, T, D, N, f_shift, seed, dtype=torch.bfloat16):
 
 @pytest.mark.parametrize("cfg", [(8, 16384, 2048, 16, 2.0), (4, 65536, 2048, 16, 4.0)])
 def test_full_size_properties(cfg):
-    """At BASELINE's full sizes (metric config; config 2) the oracle is out of reach, so parity
+    """At the benchmark's full sizes (metric config; config 2) the oracle is out of reach, so parity
     rests on properties that do not depend on size:
       composition  scanning [0,T) == scanning [0,s) then [s,T) from the carried state
                    (fp32 final state to 1e-5; bf16 y to the rounding-flip bound 1e-3)
