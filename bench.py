@@ -24,6 +24,20 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+
+def host_threads():
+    """Host threads this process may use (its CPU affinity, not the machine's core count)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+# The CPU legs use every host thread.  torch.distributed.run exports OMP_NUM_THREADS=1 to its
+# workers, which would silently time the OpenMP oracle on one core: set the count explicitly,
+# before any OpenMP runtime is loaded.
+os.environ["OMP_NUM_THREADS"] = str(host_threads())
+
 METRIC = "scan fwd+bwd tokens/sec and HBM GB/s % of peak, B=8 L=16K D=2048 N=16"
 CFG = dict(B=8, T=16384, D=2048, N=16)
 FALLBACK_HBM_GBS = 6650.0
@@ -128,6 +142,42 @@ def cpu_reference_run(steps, warmup, target_s=2.5):
     return value, ms, cores, sample
 
 
+def reference_python_run():
+    """The reference's own `naju_scan_reference` (naju/scan.py:79-93) forward + autograd backward at
+    its CPU-runnable configuration (B=2, T=512, D=64, N=16, fp32, seed 0): median of 5 after one
+    warm-up, all host threads.  Only where the reference tree can be imported (NAJU_REFERENCE_PATH);
+    returns None elsewhere."""
+    path = os.environ.get("NAJU_REFERENCE_PATH")
+    if not path or not os.path.isdir(os.path.join(path, "naju")):
+        return None
+    import torch
+    sys.path.insert(0, path)
+    try:
+        from naju.scan import naju_scan_reference
+    except Exception:
+        return None
+    finally:
+        sys.path.remove(path)
+    torch.set_num_threads(host_threads())
+    B, T, D, N = 2, 512, 64, 16
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: torch.randn(*s, generator=g)
+    u, fl, il = r(B, T, D), r(B, T, D) + 2.0, r(B, T, D)
+    Bm, Cm, dy = r(B, T, N) / N ** 0.5, r(B, T, N) / N ** 0.5, r(B, T, D)
+    leaves = [t.requires_grad_(True) for t in (u, fl, il, Bm, Cm)]
+    times = []
+    for k in range(6):
+        for t in leaves:
+            t.grad = None
+        t0 = time.perf_counter()
+        naju_scan_reference(*leaves, torch.zeros(D)).backward(dy)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times[1:])
+    return {"value": B * T / med, "unit": "tokens/s", "cores": torch.get_num_threads(),
+            "sample": "naju_scan_reference fwd+bwd, B=2,T=512,D=64,N=16 fp32, median of 5 after 1 warm-up",
+            "torch": torch.__version__}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -145,17 +195,22 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    ref_py = reference_python_run()
+    if ref_py is not None:
+        line["cpu_baseline"]["reference_python"] = ref_py
     print(json.dumps(line), flush=True)
 
 
 def ncu_traffic_bwd(B, T, D, N):
-    """DRAM bytes of one tensor-core backward launch, from the ncu capture summarised in
-    profiles/tensor_core_kernels_B8_T2048_D2048_N16.md: 497 MB for 16384 tokens at D=2048, N=16
-    (dram__bytes.sum.per_second x gpu__time_duration).  Traffic grows in proportion to the tokens
-    (every tile moves the same bytes), so a full launch is that figure scaled by the token count."""
-    if (D, N) != (2048, 16):
+    """DRAM bytes of one tensor-core backward launch, scaled from the ncu capture recorded in
+    profiles/dram_traffic_per_token.txt (JSON: bytes per token of the captured small case, keyed
+    by "D,N").  Traffic grows in proportion to the tokens (every tile moves the same bytes), so a
+    full launch is that figure times the token count.  None when no capture covers the shape."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic_per_token.txt")))
+        return float(rec["bwd_tc_kernel"][f"{D},{N}"]) * (B * T)
+    except Exception:
         return None
-    return 497.0e6 / 16384.0 * (B * T)
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -229,11 +284,24 @@ def run_gpu_arm(args):
     total_ms = t_begin.elapsed_time(t_end)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    # The reference's own protocol (naju/tests/bench_scan.py:39-54) is the median of >= 30 iterations
+    # after >= 10 warm-ups: by now at least 3 + K steps have run; time 30 more, each on its own events,
+    # and report their median beside the K-step mean.
+    evm = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(max(30, args.steps))]
+    for _ in range(max(0, 10 - args.warmup - args.steps)):
+        step()
+    for e in evm:
+        step(e)
+    barrier()
+    med = {"median_ms_per_step": statistics.median(e[0].elapsed_time(e[2]) for e in evm),
+           "median_fwd_ms": statistics.median(e[0].elapsed_time(e[1]) for e in evm),
+           "median_bwd_ms": statistics.median(e[1].elapsed_time(e[2]) for e in evm),
+           "median_over_steps": len(evm)}
 
     # ---- end to end through the public call with HOST buffers
     if args.no_e2e:
         return _finish(args, world, rank, dev, dist, torch, total_ms, None, fwd_ms, bwd_ms,
-                       sampler, 0, 0, 0)
+                       sampler, 0, 0, 0, med)
     # Inputs live in pinned host memory; the call streams batch rows through the GPU (copy in,
     # forward + backward, copy out on three streams) and leaves y and every gradient in pinned
     # host memory.  All of that is inside the timed region.
@@ -262,11 +330,11 @@ def run_gpu_arm(args):
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     d2h = sum(t.numel() * t.element_size() for t in host_out.values())
     return _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_ms, sampler,
-                   h2d, d2h, e2e_steps)
+                   h2d, d2h, e2e_steps, med)
 
 
 def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_ms, sampler, h2d,
-            d2h, e2e_steps):
+            d2h, e2e_steps, med):
     B, T, D, N = args.shape
     clocks = sampler.stop() if rank == 0 else None
     times = torch.tensor([total_ms, e2e_ms or 0.0, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
@@ -295,13 +363,15 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
                        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
                        "fwd_gbs": fwd_bytes / (fwd_ms / 1e3) / 1e9,
                        "fwd_bwd_gbs": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9,
-                       "fwd_bwd_frac_of_peak": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9 / peak},
+                       "fwd_bwd_frac_of_peak": (fwd_bytes + bwd_bytes) / (ms_per_step / 1e3) / 1e9 / peak,
+                       **med},
             "roofline": {"bound": "hbm", "kernel": "bwd_tc_kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": ncu_traffic_bwd(B, T, D, N),
                          "algorithmic_bytes_per_launch": bwd_bytes},
-            # forward + tensor-core backward + recurrent backward (stands down) + 3 finalize kernels
-            "gpu_launches": 6 * args.steps,
+            # forward, tensor-core backward, recurrent backward (stands down), 3 finalize kernels, and
+            # the failure check after the forward and after the backward
+            "gpu_launches": 8 * args.steps,
             "clocks": clocks,
         }
         if e2e_steps:
@@ -314,6 +384,9 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
             v, ms, cores, sample = cpu_reference_run(3, 1, target_s=2.0)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
                                     "sample": sample}
+            ref_py = reference_python_run()
+            if ref_py is not None:
+                line["cpu_baseline"]["reference_python"] = ref_py
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

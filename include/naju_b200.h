@@ -12,7 +12,10 @@
  *  - Return value: 0 = ok, negative = rejected argument (NAJU_E_*), positive =
  *    CUDA runtime error code of the failed launch.  Device-side conditions (a
  *    bounded wait that ran out) are recorded in the workspace status word and
- *    read back with naju_b200_read_status().
+ *    read back with naju_b200_read_status().  They are never silent: a call whose
+ *    status word ends non-zero overwrites its own outputs with NaN before it
+ *    completes (on the device, no host synchronisation), and a backward given the
+ *    checkpoints of such a forward does the same.
  *  - Shapes follow naju/scan.py:3-12: u, f_logit, i_logit, y [B,T,D];
  *    Bm, Cm [B,T,N]; D_skip [D]; states [B,D,N] fp32.  The sigmoid of both gate
  *    logits is applied inside (naju/scan.py:81-82).
@@ -41,7 +44,8 @@ enum {
   NAJU_E_STRIDE = -4,    /* inner stride not 1 / row stride smaller than the row */
   NAJU_E_WORKSPACE = -5, /* workspace too small or misaligned */
   NAJU_E_ALIGN = -6,     /* a pointer is not aligned to its element size */
-  NAJU_E_TOO_LARGE = -7  /* problem needs more workspace than naju_b200_fwd_noalloc() owns */
+  NAJU_E_TOO_LARGE = -7, /* problem needs more workspace than naju_b200_fwd_noalloc() owns */
+  NAJU_E_UNSUPPORTED = -8 /* NAJU_FLAG_CHUNKED_ONLY was set and no tensor-core kernel takes the problem */
 };
 
 /* device-side status bits, OR-ed into the workspace status word */
@@ -55,8 +59,23 @@ enum {
 
 /* desc->flags */
 enum {
-  NAJU_FLAG_RECURRENT_ONLY = 1 /* always take the exact recurrent kernels, never the
-                                  tensor-core chunked form */
+  NAJU_FLAG_RECURRENT_ONLY = 1, /* always take the exact recurrent kernels, never the
+                                   tensor-core chunked form */
+  NAJU_FLAG_CHUNKED_ONLY = 2,   /* forward: fail with NAJU_E_UNSUPPORTED instead of falling back
+                                   when no tensor-core kernel takes the problem (ignored by the
+                                   backward, whose kernel follows from how the forward ran) */
+  NAJU_FLAG_INJECT_TIMEOUT = 4  /* fault injection for tests: behave as if a bounded device-side
+                                   wait had run out (sets NAJU_ST_LOOKBACK_TIMEOUT after the
+                                   kernels; nothing on the device actually waits or hangs) */
+};
+
+/* which kernel family did the work of a call (naju_b200_read_form) */
+enum {
+  NAJU_FORM_NONE = 0,      /* nothing ran (empty problem) */
+  NAJU_FORM_RECURRENT = 1, /* exact recurrent kernels */
+  NAJU_FORM_TC_TICKET = 2, /* tensor-core chunked forward, tiles by ticket with look-back carry */
+  NAJU_FORM_TC_WALK = 3    /* tensor-core chunked form walking each channel tile along time
+                              (forward) or in reverse time (backward) */
 };
 
 /* Problem description shared by forward and backward.
@@ -155,8 +174,13 @@ int naju_b200_step(const naju_scan_desc* desc, float* state, const void* u, cons
  *   - Problems with naju_b200_ckpt_bytes() + naju_b200_fwd_scratch_bytes() above that size
  *     are rejected with NAJU_E_TOO_LARGE (B*T*D up to about 15 M token-channels at
  *     N <= 16 fits).
- *   - The first call on each device looks the array's address up (with that device current);
- *     make that first call outside any stream capture.
+ *   - The first call on each device looks the array's address up (with that device current).
+ *     With lazy module loading that is also when the array gets its device memory, so this one
+ *     call may take milliseconds and can fail on a device that is already full: make it once
+ *     per device at start-up, outside any stream capture.  The address is cached per device and
+ *     does not survive cudaDeviceReset().
+ *   - Device-side status and kernel form of the last call: naju_b200_noalloc_read_status(),
+ *     naju_b200_noalloc_read_form() (the scratch header is at the start of the array).
  *   - All calls on a device share the array: calls that may overlap on the GPU (different
  *     streams, or this and another thread) race on it and must be serialised by the caller.
  *     The array keeps the previous call's contents; the call clears the part that has to
@@ -172,6 +196,17 @@ int naju_b200_fwd_noalloc(const naju_scan_desc* desc, const void* u, const void*
  * backward call used (0 = clean; NAJU_ST_* bits otherwise), or a negative/positive error
  * code as above. */
 int naju_b200_read_status(const void* scratch, void* stream);
+
+/* Synchronises `stream` and returns which kernel family did the work of the forward or
+ * backward call that used this scratch buffer (NAJU_FORM_*), or a negative/positive error code.
+ * The reference picks its kernels on the host (naju/scan.py:48-72); here part of the choice is
+ * made on the device, and this is how a caller or a test sees it. */
+int naju_b200_read_form(const void* scratch, void* stream);
+
+/* The same two queries for the built-in workspace of naju_b200_fwd_noalloc() on the current
+ * device (the caller has no pointer to it).  No counterpart in the reference. */
+int naju_b200_noalloc_read_status(void* stream);
+int naju_b200_noalloc_read_form(void* stream);
 
 #ifdef __cplusplus
 }

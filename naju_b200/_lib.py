@@ -17,14 +17,19 @@ ST_BAD_TILE = 2
 ST_MMA_TIMEOUT = 4
 ST_DEEP_TILE = 8
 FLAG_RECURRENT_ONLY = 1
+FLAG_CHUNKED_ONLY = 2
+FLAG_INJECT_TIMEOUT = 4
+FORM_NONE, FORM_RECURRENT, FORM_TC_TICKET, FORM_TC_WALK = 0, 1, 2, 3
 E_TOO_LARGE = -7
+E_UNSUPPORTED = -8
 NOALLOC_BYTES = 32 << 20
 
 # every symbol include/naju_b200.h declares
 EXPORTS = ("naju_b200_version", "naju_b200_strerror", "naju_b200_chunk_len",
            "naju_b200_ckpt_bytes", "naju_b200_ckpt_decay_offset", "naju_b200_fwd_scratch_bytes", "naju_b200_bwd_scratch_bytes",
            "naju_b200_fwd", "naju_b200_bwd", "naju_b200_step", "naju_b200_read_status",
-           "naju_b200_fwd_noalloc")
+           "naju_b200_fwd_noalloc", "naju_b200_read_form", "naju_b200_noalloc_read_status",
+           "naju_b200_noalloc_read_form")
 
 
 class ScanDesc(ctypes.Structure):
@@ -71,8 +76,12 @@ def load():
     lib.naju_b200_step.argtypes = [dp] + [vp] * 9
     lib.naju_b200_fwd_noalloc.restype = ctypes.c_int
     lib.naju_b200_fwd_noalloc.argtypes = [dp] + [vp] * 10
-    lib.naju_b200_read_status.restype = ctypes.c_int
-    lib.naju_b200_read_status.argtypes = [vp, vp]
+    for name in ("naju_b200_read_status", "naju_b200_read_form"):
+        getattr(lib, name).restype = ctypes.c_int
+        getattr(lib, name).argtypes = [vp, vp]
+    for name in ("naju_b200_noalloc_read_status", "naju_b200_noalloc_read_form"):
+        getattr(lib, name).restype = ctypes.c_int
+        getattr(lib, name).argtypes = [vp]
     if lib.naju_b200_version() != ABI_VERSION:
         raise RuntimeError("libnaju_b200.so was built against another ABI version; rebuild it")
     _lib = lib

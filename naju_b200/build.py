@@ -16,7 +16,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libnaju_b200.so")
 
-SOURCES = ["api.cu", "fwd_simt.cu", "fwd_tc.cu", "fwd_tc2.cu", "fwd_tc3.cu", "bwd_simt.cu", "bwd_tc.cu", "step.cu", "fwd_noalloc.cu"]
+SOURCES = ["api.cu", "fwd_simt.cu", "fwd_tc2.cu", "fwd_tc3.cu", "bwd_simt.cu", "bwd_tc.cu", "step.cu", "fwd_noalloc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
 

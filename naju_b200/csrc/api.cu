@@ -20,7 +20,9 @@ int check_desc(const naju_scan_desc* d, bool need_T) {
   if (d->B < 0 || d->D < 0 || d->N < 1 || d->N > 128 || (need_T && d->T < 0)) return NAJU_E_SHAPE;
   if (!dtype_ok(d->act_dtype) || !dtype_ok(d->gate_dtype) || !dtype_ok(d->bc_dtype)) return NAJU_E_DTYPE;
   if (!(d->gate_dtype == d->act_dtype || d->gate_dtype == NAJU_F32)) return NAJU_E_DTYPE;
-  if ((d->flags & ~NAJU_FLAG_RECURRENT_ONLY) != 0) return NAJU_E_SHAPE;
+  if ((d->flags & ~(NAJU_FLAG_RECURRENT_ONLY | NAJU_FLAG_CHUNKED_ONLY | NAJU_FLAG_INJECT_TIMEOUT)) != 0)
+    return NAJU_E_SHAPE;
+  if ((d->flags & NAJU_FLAG_RECURRENT_ONLY) && (d->flags & NAJU_FLAG_CHUNKED_ONLY)) return NAJU_E_SHAPE;
   return NAJU_OK;
 }
 
@@ -46,6 +48,64 @@ __global__ void copy_state_kernel(const float* __restrict__ src, float* __restri
   if (i < n) dst[i] = src ? src[i] : fill;
 }
 
+// Makes a device-side failure loud without a host round trip.  Runs after the kernels of a call,
+// on the same stream: when the call's status word is non-zero (a bounded wait ran out), or the
+// forward that wrote these checkpoints failed that way, every output of the call is overwritten
+// with all-ones bytes (NaN in fp32, bf16 and fp16 alike).  In the normal case it reads two words
+// and returns.
+struct PoisonList {
+  void* ptr[8];
+  unsigned long long bytes[8];
+  int n;
+};
+
+__global__ void poison_on_failure_kernel(ScratchHeader* hdr, int* fwd_form, int mark_trailer, int inject,
+                                         PoisonList list) {
+  __shared__ int s_bad;
+  if (threadIdx.x == 0) {
+    if (inject && blockIdx.x == 0) atomicOr(&hdr->status, NAJU_ST_LOOKBACK_TIMEOUT);
+    int st = *reinterpret_cast<volatile int*>(&hdr->status);
+    if (inject) st |= NAJU_ST_LOOKBACK_TIMEOUT;
+    const int failed_before = (!mark_trailer && fwd_form != nullptr) ? (*fwd_form & 4) : 0;
+    s_bad = (st != 0 || failed_before != 0) ? 1 : 0;
+    if (s_bad && mark_trailer && fwd_form != nullptr && blockIdx.x == 0) atomicOr(fwd_form, 4);
+  }
+  __syncthreads();
+  if (!s_bad) return;
+  for (int k = 0; k < list.n; ++k) {
+    unsigned char* p = static_cast<unsigned char*>(list.ptr[k]);
+    const unsigned long long nb = list.bytes[k];
+    for (unsigned long long i = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nb;
+         i += static_cast<unsigned long long>(gridDim.x) * blockDim.x)
+      p[i] = 0xFF;
+  }
+}
+
+void poison_add(PoisonList& l, void* p, size_t bytes) {
+  if (p != nullptr && bytes > 0 && l.n < 8) {
+    l.ptr[l.n] = p;
+    l.bytes[l.n] = bytes;
+    ++l.n;
+  }
+}
+
+int launch_poison(ScratchHeader* hdr, int* fwd_form, bool mark_trailer, bool inject, const PoisonList& l,
+                  cudaStream_t st) {
+  poison_on_failure_kernel<<<64, 256, 0, st>>>(hdr, fwd_form, mark_trailer ? 1 : 0, inject ? 1 : 0, l);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int read_header_word(const void* scratch, size_t offset, void* stream) {
+  if (!scratch) return NAJU_E_NULL;
+  int word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, static_cast<const char*>(scratch) + offset, sizeof(int),
+                                  cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return word;
+}
+
 }  // namespace
 
 extern "C" {
@@ -61,6 +121,9 @@ const char* naju_b200_strerror(int code) {
     case NAJU_E_STRIDE: return "unsupported strides (inner stride 1, row stride >= row length)";
     case NAJU_E_WORKSPACE: return "workspace missing or not 256-byte aligned";
     case NAJU_E_ALIGN: return "pointer not aligned to its element size";
+    case NAJU_E_UNSUPPORTED:
+      return "NAJU_FLAG_CHUNKED_ONLY: no tensor-core kernel takes this problem (needs 16-bit u, bf16 B/C, "
+             "N == 16, T > 0 and strides that are multiples of 16 bytes)";
     case NAJU_E_TOO_LARGE:
       return "problem too large for the built-in workspace of naju_b200_fwd_noalloc (32 MiB); "
              "use naju_b200_fwd with caller-owned workspaces";
@@ -137,15 +200,19 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   p.flags = reinterpret_cast<int*>(sc + sl.off_flags);
   p.aggP = reinterpret_cast<float*>(sc + sl.off_aggP);
   p.aggS = reinterpret_cast<float*>(sc + sl.off_aggS);
+  int rck = -1000;
   if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY)) {
-    const int rc3 = launch_fwd_tc3(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
-    if (rc3 != -1000) return rc3;
-    const int rc2 = launch_fwd_tc2(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
-    if (rc2 != -1000) return rc2;
-    if (fwd_tc_supported(g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype))
-      return launch_fwd_tc(p, g, desc->act_dtype, desc->gate_dtype, stream);
+    rck = launch_fwd_tc3(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
+    if (rck == -1000) rck = launch_fwd_tc2(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
+    if (rck == -1000 && (desc->flags & NAJU_FLAG_CHUNKED_ONLY)) return NAJU_E_UNSUPPORTED;
   }
-  return launch_fwd_simt(p, g, desc->act_dtype, desc->gate_dtype, stream);
+  if (rck == -1000) rck = launch_fwd_simt(p, g, desc->act_dtype, desc->gate_dtype, stream);
+  if (rck != 0) return rck;
+  PoisonList pl = {};
+  poison_add(pl, y, static_cast<size_t>(desc->B) * desc->T * desc->D * dtype_size(desc->act_dtype));
+  poison_add(pl, hT, static_cast<size_t>(nstate) * 4);
+  poison_add(pl, pT, static_cast<size_t>(nchan) * 4);
+  return launch_poison(p.hdr, p.fwd_form, true, (desc->flags & NAJU_FLAG_INJECT_TIMEOUT) != 0, pl, st);
 }
 
 int naju_b200_bwd(const naju_scan_desc* desc, const void* u, const void* f_logit,
@@ -201,7 +268,19 @@ int naju_b200_bwd(const naju_scan_desc* desc, const void* u, const void* f_logit
     if (rc2 == 0) p.tc_launched = 1;
     else if (rc2 != -1000) return rc2;
   }
-  return launch_bwd_simt(p, g, desc->act_dtype, desc->gate_dtype, dB, dC, dD, stream);
+  const int rcs = launch_bwd_simt(p, g, desc->act_dtype, desc->gate_dtype, dB, dC, dD, stream);
+  if (rcs != 0) return rcs;
+  PoisonList pl = {};
+  const size_t ntd = static_cast<size_t>(desc->B) * desc->T * desc->D;
+  const size_t ntn = static_cast<size_t>(desc->B) * desc->T * desc->N;
+  poison_add(pl, du, ntd * dtype_size(desc->act_dtype));
+  poison_add(pl, dfl, ntd * dtype_size(desc->gate_dtype));
+  poison_add(pl, dil, ntd * dtype_size(desc->gate_dtype));
+  poison_add(pl, dB, ntn * dtype_size(desc->bc_dtype));
+  poison_add(pl, dC, ntn * dtype_size(desc->bc_dtype));
+  poison_add(pl, dD, static_cast<size_t>(desc->D) * 4);
+  poison_add(pl, dh0, static_cast<size_t>(desc->B) * desc->D * desc->N * 4);
+  return launch_poison(p.hdr, const_cast<int*>(p.fwd_form), false, (desc->flags & NAJU_FLAG_INJECT_TIMEOUT) != 0, pl, st);
 }
 
 int naju_b200_step(const naju_scan_desc* desc, float* state, const void* u, const void* f_logit,
@@ -219,14 +298,11 @@ int naju_b200_step(const naju_scan_desc* desc, float* state, const void* u, cons
 }
 
 int naju_b200_read_status(const void* scratch, void* stream) {
-  if (!scratch) return NAJU_E_NULL;
-  int status = 0;
-  cudaError_t e = cudaMemcpyAsync(&status, scratch, sizeof(int), cudaMemcpyDeviceToHost,
-                                  static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return static_cast<int>(e);
-  e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return static_cast<int>(e);
-  return status;
+  return read_header_word(scratch, offsetof(ScratchHeader, status), stream);
+}
+
+int naju_b200_read_form(const void* scratch, void* stream) {
+  return read_header_word(scratch, offsetof(ScratchHeader, form), stream);
 }
 
 }  // extern "C"

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
   if (p.tc_launched && (*p.fwd_form & 3) == 1) return;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (blockIdx.x == 0 && tid == 0) p.hdr->form = NAJU_FORM_RECURRENT;
   // Persistent CTAs: each takes tile tickets (reverse-time-major, so the chunk a tile waits on is
   // always held by a running CTA or done) until they run out.  The grid is a few CTAs per SM, which
   // also makes the stand-down above cost a few microseconds instead of one CTA launch per tile.

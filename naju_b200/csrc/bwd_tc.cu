@@ -34,6 +34,7 @@
 #include "common.cuh"
 #include "params.h"
 #include "tc_common.cuh"
+#include "tma_host.h"
 
 namespace naju {
 namespace tcb {
@@ -162,6 +163,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
   const int nchunks = p.nchunks;
 
   if (tid == 0) {
+    if (blockIdx.x == 0) p.hdr->form = NAJU_FORM_TC_WALK;
     for (int i = 0; i < RING; ++i) {
       mbar_init(smem_u32(&bars.full[i]), 1);
       mbar_init(smem_u32(&bars.empty[i]), NMAIN);
@@ -857,71 +859,17 @@ namespace naju {
 #endif
 
 // ------------------------------------------------------------------------------ host side
-namespace {
-
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn_b() {
-  static EncodeFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(sym);
-  }
-  return fn;
-}
-
-bool make_map_b(CUtensorMap* m, const void* base, int dt, int64_t B, int64_t T, int64_t inner, int64_t sb,
-                int64_t st, int box_inner, int box_t) {
-  const int es = dt == NAJU_F32 ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
-  if ((st * es) % 16 != 0 || (sb * es) % 16 != 0 || (box_inner * es) % 16 != 0) return false;
-  if (B > 1 && sb < st) return false;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(st * es), static_cast<cuuint64_t>((B > 1 ? sb : st * T) * es)};
-  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_t), 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  EncodeFn fn = encode_fn_b();
-  if (!fn) return false;
-  return fn(m,
-            dt == NAJU_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                           : (dt == NAJU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16),
-            3,
-            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-int sm_count_b() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
-}  // namespace
-
 // Launches the tensor-core backward for this problem if it can take it; returns -1000 if not.
 // The kernel itself stands down unless *fwd_form says the forward ran chunked without deep tiles.
 namespace {
 template <typename TA, typename TG>
 int launch_bwd_tc_t(const BwdParams& p, const tcb::Maps& maps, const int* fwd_form, int64_t ctiles, cudaStream_t st) {
   constexpr size_t smem = tcb::SmemT<TG>::total;
-  const bool multi = ctiles > sm_count_b();
+  const bool multi = ctiles > tmah::sm_count();
   auto kern = multi ? tcb::bwd_tc_kernel<TA, TG, true> : tcb::bwd_tc_kernel<TA, TG, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
-  const int64_t grid = std::min<int64_t>(ctiles, sm_count_b());
+  const int64_t grid = std::min<int64_t>(ctiles, tmah::sm_count());
   kern<<<static_cast<unsigned>(grid), tcb::NTHREADS, smem, st>>>(p, maps, fwd_form);
   return static_cast<int>(cudaGetLastError());
 }
@@ -935,21 +883,21 @@ int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int 
   const int64_t ctiles = static_cast<int64_t>(g.B) * g.ndt;
   // One persistent CTA per SM walks whole channel tiles: with fewer than about a third of the SMs
   // busy the exact recurrent backward (which spreads over time as well) is the faster one.
-  if (!(ctiles * 3 >= sm_count_b() && g.nchunks >= 4)) return -1000;
+  if (!(ctiles * 3 >= tmah::sm_count() && g.nchunks >= 4)) return -1000;
   tcb::Maps maps = {};
   const bool ok =
-      make_map_b(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB) &&
-      make_map_b(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tcb::SLAB) &&
-      make_map_b(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tcb::SLAB) &&
-      make_map_b(&maps.dy, p.dy, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::SLAB) &&
-      make_map_b(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tcb::NS, tcb::Q) &&
-      make_map_b(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q) &&
+      tmah::make_map(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB) &&
+      tmah::make_map(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tcb::SLAB) &&
+      tmah::make_map(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tcb::SLAB) &&
+      tmah::make_map(&maps.dy, p.dy, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::SLAB) &&
+      tmah::make_map(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tcb::NS, tcb::Q) &&
+      tmah::make_map(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q) &&
       // outputs are dense [B, T, D]; one 64-step x 128-channel box per store (fp32 logit gradients
       // are written from registers, not by TMA)
-      make_map_b(&maps.du, p.du, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q) &&
+      tmah::make_map(&maps.du, p.du, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q) &&
       (gate == NAJU_F32 ||
-       (make_map_b(&maps.dfl, p.dfl, gate, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q) &&
-        make_map_b(&maps.dil, p.dil, gate, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q)));
+       (tmah::make_map(&maps.dfl, p.dfl, gate, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q) &&
+        tmah::make_map(&maps.dil, p.dil, gate, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::Q)));
   if (!ok) return -1000;
   if (gate == NAJU_F32)
     return launch_bwd_tc_t<__nv_bfloat16, float>(p, maps, fwd_form, ctiles, static_cast<cudaStream_t>(stream));

@@ -11,6 +11,16 @@
 // The price: the array has a fixed size (NAJU_B200_NOALLOC_BYTES; every GPU that loads the
 // library holds it until the process exits), larger problems are rejected, and all calls on
 // a device share it.
+//
+// Layout inside the array: the forward's scratch first (so its 256-byte header, with the status
+// word, sits at offset 0 whatever the problem size, where naju_b200_noalloc_read_status() finds
+// it), then the chunk-boundary states.
+//
+// The array is part of the library's device image.  With CUDA's lazy module loading that image is
+// loaded (and the array backed by device memory) by the first call that touches it on a device,
+// so that first call may take milliseconds and may fail when the device is already full: make it
+// once per device at start-up, outside any stream capture.  The resolved address is cached per
+// device ordinal and does not survive cudaDeviceReset().
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -56,8 +66,8 @@ extern "C" int naju_b200_fwd_noalloc(const naju_scan_desc* desc, const void* u, 
                                      void* stream) {
   if (desc == nullptr) return NAJU_E_NULL;
   if (desc->N < 1 || desc->N > 128 || desc->B < 0 || desc->T < 0 || desc->D < 0) return NAJU_E_SHAPE;
-  const size_t ck = align256(naju_b200_ckpt_bytes(desc));
-  const size_t sc = naju_b200_fwd_scratch_bytes(desc);
+  const size_t ck = naju_b200_ckpt_bytes(desc);
+  const size_t sc = align256(naju_b200_fwd_scratch_bytes(desc));
   if (ck + sc > static_cast<size_t>(NAJU_B200_NOALLOC_BYTES)) return NAJU_E_TOO_LARGE;
   void* base = nullptr;
   const int rc = workspace_for_current_device(&base);
@@ -66,6 +76,22 @@ extern "C" int naju_b200_fwd_noalloc(const naju_scan_desc* desc, const void* u, 
   // naju_b200_fwd() clears the part of the scratch that must start at zero (status word, tile
   // ticket, chunk flags) with cudaMemsetAsync on `stream`; everything else is written before it
   // is read, so what the previous call left behind is harmless.
-  return naju_b200_fwd(desc, u, f_logit, i_logit, Bm, Cm, D_skip, h0, y, hT, nullptr, ws, ws + ck,
+  return naju_b200_fwd(desc, u, f_logit, i_logit, Bm, Cm, D_skip, h0, y, hT, nullptr, ws + sc, ws,
                        stream);
+}
+
+// Status word / kernel form of the last naju_b200_fwd_noalloc() call on the current device
+// (synchronises `stream`).  A device on which the entry point has not run yet reports 0.
+extern "C" int naju_b200_noalloc_read_status(void* stream) {
+  void* base = nullptr;
+  const int rc = workspace_for_current_device(&base);
+  if (rc != NAJU_OK) return rc;
+  return naju_b200_read_status(base, stream);
+}
+
+extern "C" int naju_b200_noalloc_read_form(void* stream) {
+  void* base = nullptr;
+  const int rc = workspace_for_current_device(&base);
+  if (rc != NAJU_OK) return rc;
+  return naju_b200_read_form(base, stream);
 }

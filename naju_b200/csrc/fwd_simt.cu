@@ -29,7 +29,10 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const FwdParams p) {
   __shared__ unsigned int s_ticket;
 
   const int tid = threadIdx.x;
-  if (tid == 0) s_ticket = atomicAdd(&p.hdr->ticket, 1u);
+  if (tid == 0) {
+    s_ticket = atomicAdd(&p.hdr->ticket, 1u);
+    if (blockIdx.x == 0) p.hdr->form = NAJU_FORM_RECURRENT;
+  }
   __syncthreads();
   TileCoord tc;
   if (!decode_tile<TC>(s_ticket, p.B, p.T, p.D, p.nchunks, p.ndt, tid, tc)) {

@@ -39,6 +39,7 @@
 
 #include "fwd_common.cuh"
 #include "tc_common.cuh"
+#include "tma_host.h"
 
 namespace naju {
 namespace tc3 {
@@ -217,7 +218,10 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     mbar_init(smem_u32(&bars.h_ready), NHALF);
     for (int i = 0; i < NSTAGE; ++i) mbar_init(smem_u32(&bars.d1_full[i]), 1);
     mbar_init_fence();
-    if (blockIdx.x == 0) atomicOr(p.fwd_form, 1);  // tell the backward how the forward ran
+    if (blockIdx.x == 0) {
+      atomicOr(p.fwd_form, 1);  // tell the backward how the forward ran
+      p.hdr->form = NAJU_FORM_TC_WALK;
+    }
   }
   if (warp == 0) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
   // the upper triangle of g1/g2 is never written again: clear the shared operands once
@@ -684,58 +688,6 @@ namespace naju {
 // ------------------------------------------------------------------------------ host side
 namespace {
 
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                             CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn3() {
-  static EncodeFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(sym);
-  }
-  return fn;
-}
-
-CUtensorMapDataType tm_dtype(int dt) {
-  return dt == NAJU_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                        : dt == NAJU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-}
-
-// [B][T][inner] tensor with element strides (sb, st, 1); box = (box_inner, box_t, 1)
-bool make_map3(CUtensorMap* m, const void* base, int dt, int64_t B, int64_t T, int64_t inner, int64_t sb,
-              int64_t st, int box_inner, int box_t) {
-  const int es = dt == NAJU_F32 ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
-  if ((st * es) % 16 != 0 || (sb * es) % 16 != 0 || (box_inner * es) % 16 != 0) return false;
-  if (B > 1 && sb < st) return false;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(st * es), static_cast<cuuint64_t>((B > 1 ? sb : st * T) * es)};
-  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_t), 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  EncodeFn fn = encode_fn3();
-  if (!fn) return false;
-  return fn(m, tm_dtype(dt), 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-int sm_count3() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 template <typename TA, typename TG>
 int launch_tc3_t(const FwdParams& p, const Geometry& g, const tc3::Maps& maps, cudaStream_t st) {
   const size_t smem = tc3::Smem<TG>::total;
@@ -743,7 +695,7 @@ int launch_tc3_t(const FwdParams& p, const Geometry& g, const tc3::Maps& maps, c
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   // one persistent CTA per SM; channel tiles are dealt round-robin
-  const int64_t grid = std::min<int64_t>(static_cast<int64_t>(g.B) * g.ndt, sm_count3());
+  const int64_t grid = std::min<int64_t>(static_cast<int64_t>(g.B) * g.ndt, tmah::sm_count());
   kern<<<static_cast<unsigned>(grid), tc3::NTHREADS, smem, st>>>(p, maps);
   return static_cast<int>(cudaGetLastError());
 }
@@ -759,15 +711,15 @@ int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act, int gate, int
   if (g.ntiles >= (1LL << 31)) return -1000;
   // (with fewer than about a third of the SMs busy the ticket-mode kernel, which spreads over time as
   // well, is the faster one)
-  if (static_cast<int64_t>(g.B) * g.ndt * 3 < sm_count3() || g.nchunks < 4) return -1000;
+  if (static_cast<int64_t>(g.B) * g.ndt * 3 < tmah::sm_count() || g.nchunks < 4) return -1000;
   tc3::Maps maps;
   const bool ok =
-      make_map3(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tc3::SLAB) &&
-      make_map3(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tc3::SLAB) &&
-      make_map3(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tc3::SLAB) &&
-      make_map3(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tc3::NS, tc3::Q) &&
-      make_map3(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tc3::NS, tc3::Q) &&
-      make_map3(&maps.y, p.y, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tc3::Q);
+      tmah::make_map(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tc3::SLAB) &&
+      tmah::make_map(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tc3::SLAB) &&
+      tmah::make_map(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tc3::SLAB) &&
+      tmah::make_map(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tc3::NS, tc3::Q) &&
+      tmah::make_map(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tc3::NS, tc3::Q) &&
+      tmah::make_map(&maps.y, p.y, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tc3::Q);
   if (!ok) return -1000;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (act == NAJU_BF16 && gate == NAJU_BF16) return launch_tc3_t<__nv_bfloat16, __nv_bfloat16>(p, g, maps, st);

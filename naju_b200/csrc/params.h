@@ -37,6 +37,8 @@ inline Geometry make_geometry(const naju_scan_desc& d) {
 // Trailer of the checkpoint buffer: how the forward ran, for the backward's kernel choice.
 //   bit 0  the forward ran in the tensor-core chunked form, walking each channel tile in time
 //   bit 1  it met at least one deep-gate tile (the factorised backward cannot take those)
+//   bit 2  a bounded wait of the forward ran out: its outputs were overwritten with NaN, and the
+//          backward of these checkpoints does the same to its own
 struct CkptTrailer {
   int fwd_form;
 };
@@ -57,6 +59,7 @@ inline CkptLayout ckpt_layout(const Geometry& g) {
 struct ScratchHeader {
   int status;            // NAJU_ST_* bits
   unsigned int ticket;   // dynamic tile counter
+  int form;              // NAJU_FORM_* of the kernel that did the work (written by that kernel)
 };
 
 // Forward scratch: header | flags[ntiles] | aggP[ntiles][128] | aggS[ntiles][128][NS]
@@ -140,8 +143,6 @@ struct BwdParams {
 // launchers implemented in the .cu files; return a CUDA runtime error code (0 = ok)
 int launch_fwd_simt(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype,
                     void* stream);
-bool fwd_tc_supported(const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype);
-int launch_fwd_tc(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, void* stream);
 // TMA-fed persistent tensor-core forward; returns -1000 when the problem cannot take it
 int launch_fwd_tc2(const FwdParams& p, const Geometry& g, int act_dtype, int gate_dtype, int bc_dtype,
                    void* stream);

@@ -34,7 +34,8 @@ def resolve_backend(backend=None):
 def _form():
     """NAJU_B200_FORM selects the forward kernel family: "auto" (default) takes the tcgen05
     tensor-core chunked form where it applies (16-bit activations, bf16 B/C, N == 16, TMA-legal
-    strides) and the exact recurrent kernels elsewhere; "recurrent" forces the recurrent ones."""
+    strides) and the exact recurrent kernels elsewhere; "recurrent" forces the recurrent ones;
+    "chunked" insists on the tensor-core form and raises where it does not apply."""
     f = os.environ.get("NAJU_B200_FORM", "auto").lower()
     if f not in ("auto", "chunked", "recurrent"):
         raise ValueError(f"NAJU_B200_FORM must be 'auto', 'chunked' or 'recurrent', got {f!r}")
@@ -43,6 +44,16 @@ def _form():
 
 def _check_status_enabled():
     return os.environ.get("NAJU_B200_CHECK_STATUS", "0") == "1"
+
+
+# Kernel family (FORM_* of _lib) that did the work of the last forward / backward call, recorded
+# when NAJU_B200_CHECK_STATUS=1 (reading it synchronises the stream).
+_last_forms = {"fwd": None, "bwd": None}
+
+
+def last_kernel_forms():
+    """{"fwd": form, "bwd": form} of the most recent calls made with NAJU_B200_CHECK_STATUS=1."""
+    return dict(_last_forms)
 
 
 def _ptr(t):
@@ -90,7 +101,11 @@ def _desc(u, f_logit, i_logit, Bm, Cm):
     d = _lib.ScanDesc()
     d.B, d.T, d.D, d.N = B, T, D, Bm.shape[-1]
     d.act_dtype, d.gate_dtype, d.bc_dtype = _DT[u.dtype], _DT[f_logit.dtype], _DT[Bm.dtype]
-    d.flags = _lib.FLAG_RECURRENT_ONLY if _form() == "recurrent" else 0
+    form = _form()
+    d.flags = (_lib.FLAG_RECURRENT_ONLY if form == "recurrent" else
+               _lib.FLAG_CHUNKED_ONLY if form == "chunked" else 0)
+    if os.environ.get("NAJU_B200_INJECT_TIMEOUT", "0") == "1":  # fault injection for tests
+        d.flags |= _lib.FLAG_INJECT_TIMEOUT
     d.u_sb, d.u_st = u.stride(0), u.stride(1)
     d.fl_sb, d.fl_st = f_logit.stride(0), f_logit.stride(1)
     d.il_sb, d.il_st = i_logit.stride(0), i_logit.stride(1)
@@ -134,6 +149,7 @@ def scan_forward(u, f_logit, i_logit, Bm, Cm, D_skip, h0=None, want_final=False,
         _lib.check(rc, "naju_b200_fwd")
         if _check_status_enabled() and B * T * D > 0:
             st = lib.naju_b200_read_status(_ptr(scratch), _stream())
+            _last_forms["fwd"] = lib.naju_b200_read_form(_ptr(scratch), _stream())
             if st != 0:
                 raise RuntimeError(f"naju_b200_fwd device status {st} (bounded wait ran out)")
     return y, hT, pT, ckpt, d
@@ -162,6 +178,7 @@ def scan_backward(d, u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy, dhT, ckpt, wan
         _lib.check(rc, "naju_b200_bwd")
         if _check_status_enabled() and B * T * D > 0:
             st = lib.naju_b200_read_status(_ptr(scratch), _stream())
+            _last_forms["bwd"] = lib.naju_b200_read_form(_ptr(scratch), _stream())
             if st != 0:
                 raise RuntimeError(f"naju_b200_bwd device status {st} (bounded wait ran out)")
     return du, dfl, dil, dB, dC, dD, dh0
@@ -202,6 +219,95 @@ class _NajuB200Scan(torch.autograd.Function):
                 None if dh0 is None else dh0.to(ctx.h0_dtype), None)
 
 
+# ---------------------------------------------------------------------------------------------
+# The same forward / backward as torch.library custom ops, so that torch.compile does not break
+# the graph at the scan (the reference's scan is a graph break: naju/README.md:99-100) and
+# NajuBlock(use_ckpt=True) (naju/mixer.py:139-141) composes.  Used while compiling; eager calls
+# keep the autograd.Function above.
+def _ckpt_bytes_formula(B, T, D, N):
+    """Size of the checkpoint buffer (naju_b200_ckpt_bytes) as arithmetic that also works on the
+    symbolic sizes of fake tensors."""
+    NS = 16 if N <= 16 else 32 if N <= 32 else 64 if N <= 64 else 128
+    TC = 64 if NS <= 32 else 32
+    ntiles = ((T + TC - 1) // TC) * B * ((D + 127) // 128)
+    a256 = lambda x: (x + 255) // 256 * 256
+    return a256(ntiles * 128 * NS * 4) + a256(ntiles * 128 * 4) + 256
+
+
+@torch.library.custom_op("naju_b200::scan_fwd", mutates_args=())
+def _scan_fwd_op(u: torch.Tensor, f_logit: torch.Tensor, i_logit: torch.Tensor, Bm: torch.Tensor,
+                 Cm: torch.Tensor, D_skip: torch.Tensor, h0: torch.Tensor,
+                 want_final: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    pu, pf, pi, pB, pC, pD = _prepare(u, f_logit, i_logit, Bm, Cm, D_skip)
+    B, T, D = pu.shape
+    ph0 = _state_arg(h0, B, D, pB.shape[-1], "h0") if h0.numel() else None
+    y, hT, _, ckpt, _ = scan_forward(pu, pf, pi, pB, pC, pD, ph0, want_final=want_final)
+    return y, (hT if want_final else y.new_empty(0, dtype=torch.float32)), ckpt
+
+
+@_scan_fwd_op.register_fake
+def _(u, f_logit, i_logit, Bm, Cm, D_skip, h0, want_final):
+    B, T, D = u.shape
+    N = Bm.shape[-1]
+    hT = u.new_empty((B, D, N), dtype=torch.float32) if want_final else u.new_empty(0, dtype=torch.float32)
+    ckpt = u.new_empty(_ckpt_bytes_formula(B, T, D, N), dtype=torch.uint8)
+    return u.new_empty((B, T, D)), hT, ckpt
+
+
+@torch.library.custom_op("naju_b200::scan_bwd", mutates_args=())
+def _scan_bwd_op(u: torch.Tensor, f_logit: torch.Tensor, i_logit: torch.Tensor, Bm: torch.Tensor,
+                 Cm: torch.Tensor, D_skip: torch.Tensor, h0: torch.Tensor, dy: torch.Tensor,
+                 dhT: torch.Tensor, ckpt: torch.Tensor) -> list[torch.Tensor]:
+    pu, pf, pi, pB, pC, pD = _prepare(u, f_logit, i_logit, Bm, Cm, D_skip)
+    B, T, D = pu.shape
+    N = pB.shape[-1]
+    ph0 = _state_arg(h0, B, D, N, "h0") if h0.numel() else None
+    pdhT = _state_arg(dhT, B, D, N, "dhT") if dhT.numel() else None
+    d = _desc(pu, pf, pi, pB, pC)
+    du, dfl, dil, dB, dC, dD, dh0 = scan_backward(d, pu, pf, pi, pB, pC, pD, ph0, dy, pdhT, ckpt,
+                                                  want_dh0=ph0 is not None)
+    if dh0 is None:
+        dh0 = du.new_empty(0, dtype=torch.float32)
+    return [du.to(u.dtype), dfl.to(f_logit.dtype), dil.to(i_logit.dtype), dB.to(Bm.dtype), dC.to(Cm.dtype),
+            dD.to(D_skip.dtype), dh0.to(h0.dtype)]
+
+
+@_scan_bwd_op.register_fake
+def _(u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy, dhT, ckpt):
+    return [torch.empty_like(u, memory_format=torch.contiguous_format),
+            torch.empty_like(f_logit, memory_format=torch.contiguous_format),
+            torch.empty_like(i_logit, memory_format=torch.contiguous_format),
+            torch.empty_like(Bm, memory_format=torch.contiguous_format),
+            torch.empty_like(Cm, memory_format=torch.contiguous_format),
+            torch.empty_like(D_skip), torch.empty_like(h0)]
+
+
+def _scan_op_setup(ctx, inputs, output):
+    u, f_logit, i_logit, Bm, Cm, D_skip, h0, want_final = inputs
+    ctx.save_for_backward(u, f_logit, i_logit, Bm, Cm, D_skip, h0, output[2])
+    ctx.want_final = want_final
+
+
+def _scan_op_backward(ctx, dy, dhT, _dckpt):
+    u, f_logit, i_logit, Bm, Cm, D_skip, h0, ckpt = ctx.saved_tensors
+    if dy is None:
+        dy = torch.zeros_like(u)
+    if dhT is None or not ctx.want_final:
+        dhT = u.new_empty(0, dtype=torch.float32)
+    du, dfl, dil, dB, dC, dD, dh0 = _scan_bwd_op(u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy.contiguous(),
+                                                 dhT, ckpt)
+    return du, dfl, dil, dB, dC, dD, (dh0 if h0.numel() else None), None
+
+
+_scan_fwd_op.register_autograd(_scan_op_backward, setup_context=_scan_op_setup)
+
+
+def _scan_via_custom_op(u, f_logit, i_logit, B, C, D_skip, h0, want_final):
+    h0t = h0 if h0 is not None else u.new_empty(0, dtype=torch.float32)
+    y, hT, _ = _scan_fwd_op(u, f_logit, i_logit, B, C, D_skip, h0t, want_final)
+    return (y, hT) if want_final else y
+
+
 def naju_b200_scan(u, f_logit, i_logit, B, C, D_skip):
     """Backend callable with the reference's 6-tensor signature (naju/scan.py:3-5)."""
     return _NajuB200Scan.apply(u, f_logit, i_logit, B, C, D_skip, None, False)
@@ -216,8 +322,9 @@ def naju_scan(u, f_logit, i_logit, B, C, D_skip, backend=None, *, h0=None,
     (y, hT) where hT [B,D,N] fp32 is the state after the last step.
     """
     resolve_backend(backend)
-    out = _NajuB200Scan.apply(u, f_logit, i_logit, B, C, D_skip, h0, bool(return_final_state))
-    return out
+    if torch.compiler.is_compiling():
+        return _scan_via_custom_op(u, f_logit, i_logit, B, C, D_skip, h0, bool(return_final_state))
+    return _NajuB200Scan.apply(u, f_logit, i_logit, B, C, D_skip, h0, bool(return_final_state))
 
 
 @torch.no_grad()

@@ -123,20 +123,33 @@ def test_low_precision_io_matches_identically_rounded_oracle(dtype, gate_dtype):
         assert oracle.rel_l2(out[k], _round(g[k], gd)) < TOL_GRAD, k
 
 
-@pytest.mark.parametrize("shape", [(2, 64, 128, 16, 2.0), (2, 1000, 384, 16, 2.0), (1, 700, 200, 12, 4.0),
-                                   (1, 300, 256, 16, -3.0), (1, 300, 256, 16, -12.0),
+def _forms():
+    from naju_b200.scan import last_kernel_forms
+    return last_kernel_forms()
+
+
+TICKET, WALK, RECURRENT = 2, 3, 1   # NAJU_FORM_* of include/naju_b200.h
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 128, 16, 2.0, TICKET), (2, 1000, 384, 16, 2.0, TICKET),
+                                   (1, 300, 256, 16, -3.0, TICKET), (1, 300, 256, 16, -12.0, TICKET),
+                                   # a partial channel tile (D % 128 = 72) in the ticket kernel
+                                   (2, 1000, 200, 16, 2.0, TICKET),
                                    # enough channel tiles for the walk-along-time mode (ragged T)
-                                   (4, 520, 2432, 16, 2.0), (4, 520, 2432, 16, -2.5)])
+                                   (4, 520, 2432, 16, 2.0, WALK), (4, 520, 2432, 16, -2.5, WALK),
+                                   # ... with a partial last channel tile (D % 128 = 8)
+                                   (4, 520, 2440, 16, 2.0, WALK)])
 def test_tensor_core_chunked_forward(monkeypatch, shape):
     """The tcgen05 chunked form against the fp64 oracle on the same bf16-quantised inputs.
-    Its arithmetic error is measured on the fp32 final state (tolerance 1e-3, the build
-    target).  y is emitted in bf16, so it is compared with the oracle rounded the same way;
-    a perturbation e before that rounding moves about e/ulp of the outputs by one bf16 ulp,
-    which bounds the distance by ~sqrt(e * 2^-8): 2e-3 here.  Deep-gate tiles (f_shift <= -3)
-    take the exact per-tile path and must meet the tight bound."""
+    NAJU_B200_FORM=chunked makes the call fail rather than fall back, and the kernel family
+    that ran is read back and asserted.  The arithmetic error is measured on the fp32 final
+    state; y is emitted in bf16, so it is compared with the oracle rounded the same way (both
+    to 1e-3, the build target; a perturbation e before rounding moves about e/ulp of the
+    outputs by one bf16 ulp, i.e. ~sqrt(e * 2^-8), measured ~3.6e-4).  Deep-gate tiles
+    (f_shift <= -2.5) take the exact per-tile path and must meet the tight bound."""
     from naju_b200 import naju_scan
     monkeypatch.setenv("NAJU_B200_FORM", "chunked")
-    B, T, D, N, fs = shape
+    B, T, D, N, fs, form = shape
     dt = torch.bfloat16
     d = oracle.make_inputs(B, T, D, N, seed=3, f_shift=fs, d_skip_scale=0.01, with_h0=True)
     q = {k: (_round(d[k], dt) if k in ("u", "fl", "il", "Bm", "Cm") else d[k]) for k in d}
@@ -147,13 +160,27 @@ def test_tensor_core_chunked_forward(monkeypatch, shape):
                           return_final_state=True)
     yo, hTo = oracle.oracle_fwd(q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"], h0=q["h0"],
                                 return_final_state=True)
+    assert _forms()["fwd"] == form
     deep = fs <= -2.5
     assert oracle.rel_l2(hT.cpu().numpy(), hTo) < (TIGHT_FWD if deep else TOL_FWD)
-    assert oracle.rel_l2(y.float().cpu().numpy(), _round(yo, dt)) < (TOL_FWD if deep else 2e-3)
+    assert oracle.rel_l2(y.float().cpu().numpy(), _round(yo, dt)) < TOL_FWD
+
+
+def test_chunked_form_refuses_what_it_cannot_take(monkeypatch):
+    """NAJU_B200_FORM=chunked on a problem no tensor-core kernel takes (N = 12 is not one of
+    its state widths) must raise, not fall back."""
+    from naju_b200 import naju_scan
+    monkeypatch.setenv("NAJU_B200_FORM", "chunked")
+    z = torch.zeros(1, 70, 64, device="cuda", dtype=torch.bfloat16)
+    zn = torch.zeros(1, 70, 12, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no tensor-core kernel"):
+        naju_scan(z, z, z, zn, zn, torch.zeros(64, device="cuda"))
 
 
 @pytest.mark.parametrize("case", [(4, 256, 2432, 16, 2.0, True), (4, 520, 2432, 16, 2.0, False),
                                   (4, 520, 2432, 16, 4.0, True), (4, 520, 2432, 16, -2.5, True),
+                                  # a partial last channel tile (D % 128 = 8), with and without states
+                                  (4, 520, 2440, 16, 2.0, True), (4, 300, 2440, 16, 2.0, False),
                                   # more channel tiles than SMs (some CTAs walk two of them), and
                                   # only a third of the SMs busy
                                   (2, 300, 12800, 16, 2.0, True), (1, 260, 6400, 16, 2.0, False)])
@@ -177,6 +204,9 @@ def test_tensor_core_chunked_backward(case):
         y = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"])
         y.backward(torch.tensor(q["dy"], device="cuda").to(dt))
     torch.cuda.synchronize()
+    # the walk-along-time forward ran; the tensor-core backward did the work unless the forward
+    # met deep-gate tiles, in which case the exact recurrent backward must have
+    assert _forms() == {"fwd": WALK, "bwd": RECURRENT if fs <= -2.5 else WALK}
     a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
     g = oracle.oracle_bwd(*a, q["dy"], h0=q["h0"] if state else None, dhT=d["dhT"] if state else None)
     for k, src in GRADS:
@@ -187,7 +217,8 @@ def test_tensor_core_chunked_backward(case):
         assert oracle.rel_l2(t["h0"].grad.cpu().numpy(), g["dh0"]) < 1e-4
 
 
-@pytest.mark.parametrize("case", [(4, 256, 2432, 16, 2.0, True), (4, 520, 2432, 16, 4.0, False)])
+@pytest.mark.parametrize("case", [(4, 256, 2432, 16, 2.0, True), (4, 520, 2432, 16, 4.0, False),
+                                  (4, 300, 2440, 16, 2.0, True)])
 def test_tensor_core_fp32_logits(case):
     """The mixer's dtype mix under bf16 autocast (bf16 u, B, C; fp32 logits and logit gradients)
     through the tensor-core forward and backward: the logits are not quantised, their gradients
@@ -208,9 +239,10 @@ def test_tensor_core_fp32_logits(case):
         y.backward(torch.tensor(q["dy"], device="cuda").to(dt))
     torch.cuda.synchronize()
     assert t["fl"].grad.dtype == torch.float32 and t["il"].grad.dtype == torch.float32
+    assert _forms() == {"fwd": WALK, "bwd": WALK}
     a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
     yo = oracle.oracle_fwd(*a, h0=q["h0"] if state else None)
-    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(yo, dt)) < 2e-3
+    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(yo, dt)) < TOL_FWD
     g = oracle.oracle_bwd(*a, q["dy"], h0=q["h0"] if state else None, dhT=d["dhT"] if state else None)
     for k, src in GRADS:
         got = t[src].grad.float().cpu().numpy()
@@ -246,6 +278,7 @@ def test_tensor_core_forward_fp16(gate32):
     y, hT = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"], h0=t["h0"], return_final_state=True)
     torch.autograd.backward([y, hT], [torch.tensor(q["dy"], device="cuda").to(dt), torch.tensor(d["dhT"], device="cuda")])
     torch.cuda.synchronize()
+    assert _forms() == {"fwd": WALK, "bwd": RECURRENT}
     a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
     yo, hTo = oracle.oracle_fwd(*a, h0=q["h0"], return_final_state=True)
     assert oracle.rel_l2(hT.detach().cpu().numpy(), hTo) < TOL_FWD
@@ -259,7 +292,7 @@ def test_tensor_core_forward_fp16(gate32):
 def test_bf16_channel_count_tma_cannot_describe():
     """D = 2434 is not a multiple of 8, so the bf16 row stride is not a multiple of 16 bytes and no
     TMA descriptor exists for these tensors: the call must quietly take the kernels that do not
-    need one, with the same results."""
+    need one (here the exact recurrent kernels), with the same results."""
     from naju_b200 import naju_scan
     B, T, D, N = 4, 300, 2434, 16
     dt = torch.bfloat16
@@ -270,8 +303,9 @@ def test_bf16_channel_count_tma_cannot_describe():
     y = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"])
     y.backward(torch.tensor(q["dy"], device="cuda").to(dt))
     torch.cuda.synchronize()
+    assert _forms() == {"fwd": RECURRENT, "bwd": RECURRENT}
     a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
-    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(oracle.oracle_fwd(*a), dt)) < 2e-3
+    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(oracle.oracle_fwd(*a), dt)) < TOL_FWD
     g = oracle.oracle_bwd(*a, q["dy"])
     for k, src in GRADS:
         ref = g[k] if k == "dD" else _round(g[k], dt)

@@ -24,9 +24,10 @@ pytestmark = pytest.mark.gpu
 TIGHT_FWD = 2e-5
 
 
-def _inputs(B, T, D, N, seed):
+def _inputs(B, T, D, N, seed, dtype=torch.float32):
     d = oracle.make_inputs(B, T, D, N, seed=seed, d_skip_scale=0.01, with_h0=True)
-    return {k: torch.tensor(d[k], device="cuda") for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "h0")}
+    return {k: torch.tensor(d[k], device="cuda").to(torch.float32 if k in ("Dskip", "h0") else dtype)
+            for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "h0")}
 
 
 def _p(t):
@@ -53,6 +54,9 @@ def test_noalloc_forward_matches_caller_workspace_forward_twice(shapes):
         rc = _call_noalloc(lib, desc, t, y, hT)
         assert rc == 0, _lib.strerror(rc)
         torch.cuda.synchronize()
+        stream = torch.cuda.current_stream().cuda_stream
+        assert lib.naju_b200_noalloc_read_status(stream) == 0
+        assert lib.naju_b200_noalloc_read_form(stream) == _lib.FORM_RECURRENT
         assert oracle.rel_l2(y.cpu().numpy(), y_ref.cpu().numpy()) < TIGHT_FWD
         assert oracle.rel_l2(hT.cpu().numpy(), hT_ref.cpu().numpy()) < TIGHT_FWD
         # and against the CPU oracle, so that both entry points being wrong together shows
@@ -60,6 +64,36 @@ def test_noalloc_forward_matches_caller_workspace_forward_twice(shapes):
                                     h0=t["h0"].cpu().numpy(), return_final_state=True)
         assert oracle.rel_l2(y.cpu().numpy(), yo) < TIGHT_FWD
         assert oracle.rel_l2(hT.cpu().numpy(), hTo) < TIGHT_FWD
+
+
+def test_noalloc_forward_through_the_tensor_core_kernels_twice():
+    """bf16 problems that take the TMA / tcgen05 kernels (first the ticket kernel with its
+    look-back scratch, then the walk-along-time kernel), so that those run on the library's own
+    workspace too: both must match the caller-workspace entry point bit for bit or to rounding,
+    report a clean status word and the expected kernel family."""
+    from naju_b200 import _lib
+    from naju_b200.scan import scan_forward
+    lib = _lib.load()
+    bf = torch.bfloat16
+    stream = torch.cuda.current_stream().cuda_stream
+    for (B, T, D, N, seed, form) in [(2, 1000, 200, 16, 3, _lib.FORM_TC_TICKET),
+                                     (4, 300, 1664, 16, 4, _lib.FORM_TC_WALK)]:
+        t = _inputs(B, T, D, N, seed, dtype=bf)
+        y_ref, hT_ref, _, _, desc = scan_forward(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"],
+                                                 t["Dskip"], t["h0"], want_final=True)
+        y = torch.full_like(y_ref, float("nan"))
+        hT = torch.full_like(hT_ref, float("nan"))
+        rc = _call_noalloc(lib, desc, t, y, hT)
+        assert rc == 0, _lib.strerror(rc)
+        assert lib.naju_b200_noalloc_read_status(stream) == 0
+        assert lib.naju_b200_noalloc_read_form(stream) == form
+        # same kernel, same inputs: only the look-back's folding order may differ
+        assert oracle.rel_l2(hT.cpu().numpy(), hT_ref.cpu().numpy()) < TIGHT_FWD
+        assert oracle.rel_l2(y.float().cpu().numpy(), y_ref.float().cpu().numpy()) < 1e-3
+        yo, hTo = oracle.oracle_fwd(*(t[k].float().cpu().numpy() for k in ("u", "fl", "il", "Bm", "Cm")),
+                                    t["Dskip"].cpu().numpy(), h0=t["h0"].cpu().numpy(), return_final_state=True)
+        assert oracle.rel_l2(hT.cpu().numpy(), hTo) < 1e-3
+        assert oracle.rel_l2(y.float().cpu().numpy(), torch.tensor(yo).to(bf).float().numpy()) < 1e-3
 
 
 def test_noalloc_rejects_problems_beyond_its_workspace():
