@@ -1,5 +1,5 @@
 // Forward gated scan, chunked (state-expansion) form: persistent, TMA-fed, warp-specialised,
-// tcgen05/TMEM, two threads per channel.
+// tcgen05/TMEM, four threads per channel.
 //
 // Math (per chunk of Q = 64 steps, channel d; P_t = prod_{r<=t} f_r, R_t = 1/P_t,
 // wt_s = sigmoid(i_s) u_s R_s; recurrence of naju/scan.py:79-93, contraction of
@@ -14,26 +14,29 @@
 // bits; the dropped w2.g2 term is 2^-16 relative), so the tensor-core path keeps ~1e-5 accuracy.
 //
 // One persistent CTA per SM walks channel tiles (one batch row x 128 channels) along time, so
-// the carry never leaves the chip.  Twenty warps in five roles, two pipeline stages (operand
-// rows, shared operands and TMEM accumulators are double buffered):
-//   warp 16     TMA producer: u / f_logit / i_logit in 16-step slabs through a 4-deep mbarrier
-//               ring, plus the chunk's B and C rows and a second copy of u for the epilogue.
-//   warps 8-15  gate warps, two threads per channel (steps 0-31 / 32-63 of the chunk; the second
-//               thread first multiplies up the retention of steps 0-31 to enter step 32 with
-//               the right product): sigmoids, running products, the channel's operand row
-//               (K-major, no swizzle) and P_t, which goes to TMEM with tcgen05.st.
-//   warps 17-18 operand builders: C | g1 | g2 and B^T of the tile with mma.sync (16x8 blocks of G dealt
-//               round-robin), started as soon as the MMAs of the tile two back have read the stage.
-//   warp 19     MMA issuer: one thread issues every tcgen05.mma, slab by slab as the gate warps
+// the carry never leaves the chip.  Twenty-five warps in six roles; operand rows, shared operands
+// and TMEM accumulators are double buffered (two pipeline stages):
+//   warps 0-15  main warps, four threads per channel: group g = warp / 4 owns steps [16g, 16g+16) of
+//               every chunk.  Per tile a thread (1) multiplies up the retention of its own 16
+//               steps and publishes the product, (2) finishes the PREVIOUS tile for the same
+//               steps -- y_t = P_t D1[d][t] (+ D_skip u_t) from TMEM into the staging tile; P_t is
+//               still in its registers, so it never travels -- and (3) picks up the products of
+//               the groups before it, which gives R_t, and writes its part of the channel's
+//               operand row (K-major, no swizzle).  No thread repeats another thread's work.
+//   warps 16-19 carry warps (thread = channel): D2 -> next chunk's carry-in (registers), the
+//               checkpoint, and the carry-in operand row, posted one tile ahead; deep-gate tiles.
+//   warps 20-21 operand builders: the chunk's C and B rows into operand layout, G = C B^T by one
+//               tcgen05.mma of their own (M = time), read back from TMEM row by row (lane = step t),
+//               masked to s <= t, split in two bf16 terms and written as the rows [C | g1 | g2].
+//   warp 22     TMA producer: u / f_logit / i_logit in 16-step slabs (one per group) through an
+//               mbarrier ring, and the chunk's raw B and C rows.
+//   warp 23     MMA issuer: one thread issues every tcgen05.mma, slab by slab as the groups
 //               deliver, and every tcgen05.commit.
-//   warps 0-7   carry/epilogue warps: warps 0-3 turn D2 into the next chunk's carry-in (registers),
-//               write the checkpoint and post the carry-in row one tile ahead; all eight read
-//               y_t = P_t D1[d][t] back from TMEM (lane = channel, 16 / 48 columns per thread),
-//               add D_skip u_t (u is kept in shared memory for this), stage the tile in shared
-//               memory and hand it to a TMA store.
+//   warp 24     store warp: hands a finished staging tile to a TMA store and releases the stage
+//               when the store has read it, so no compute warp ever waits for a store.
 // A tile whose retention product falls below 2^-80 in any channel (deep gates) cannot use the
-// 1/P_t factorisation; warps 0-3 then run the exact recurrence for that tile straight from global
-// memory, from the carry they hold.  Every wait is bounded.
+// 1/P_t factorisation; the carry warps then run the exact recurrence for that tile straight from
+// global memory, from the carry they hold.  Every wait is bounded.
 #include <algorithm>
 #include <type_traits>
 
@@ -46,29 +49,43 @@ namespace tc3 {
 
 using namespace tcx;
 
-constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, RING = 4, NSTAGE = 2;
-// NGRP gate groups of 128 threads: group g owns the steps of slabs [g * NSLAB / NGRP, (g + 1) * NSLAB / NGRP)
-constexpr int NGRP = 2, SPG = NSLAB / NGRP;  // (four groups measured slower: 0.89 ms against 0.83 ms)
-// NBUILD operand-builder warps share a tile's work (one warp alone takes 5.5 k cycles per tile, longer
-// than the gate warps; with two the MMA issuer no longer waits for operands; four measured slower)
-constexpr int NBUILD = 2;
-constexpr int NHALF = 128, NGATE = NGRP * 128, NEPI = 256, NTHREADS = NEPI + NGATE + 32 * (2 + NBUILD);
-constexpr int W_PROD = (NEPI + NGATE) / 32, W_BUILD = W_PROD + 1, W_MMA = W_BUILD + NBUILD;
+constexpr int Q = 64, NS = 16, SLAB = 16, NSLAB = Q / SLAB, NSTAGE = 2;
+#ifndef NAJU_RING16
+#define NAJU_RING16 7
+#endif
+constexpr int RING_MAX = 8;                 // input-slab ring: as deep as shared memory allows (see Smem)
+constexpr int NGRP = NSLAB;                 // main-warp groups: one slab of every chunk each
+constexpr int NBUILD = 2;                   // operand-builder warps sharing a tile's work
+constexpr int NHALF = 128, NMAIN = NGRP * 128, NCARRY = 128;
+// (builder warp k reads accumulator rows 32k .. 32k+31: its index must be k modulo 4)
+constexpr int W_CARRY = NMAIN / 32, W_BUILD = W_CARRY + NCARRY / 32, W_PROD = W_BUILD + NBUILD,
+              W_MMA = W_PROD + 1, W_STORE = W_MMA + 1, NTHREADS = 32 * (W_STORE + 1);
+static_assert(W_BUILD % 4 == 0 && NBUILD == 2, "builder warps sit on TMEM lane quarters 0 and 1");
 constexpr int AW_W1 = 0, AW_W2 = 8;
 constexpr uint32_t SBO_AW = 16 * 128, AW_BYTES = 16 * SBO_AW;  // operand rows [w1 64 | w2 64], per stage
 constexpr int AH_H1 = 0, AH_H2 = 2;
 constexpr uint32_t SBO_AH = 4 * 128, AH_BYTES = 16 * SBO_AH;   // carry-in rows [h1 16 | h2 16]
 constexpr int B1_C = 0, B1_G1 = 2, B1_G2 = 10;
 constexpr uint32_t SBO_B1 = 18 * 128, B1_BYTES = 8 * SBO_B1;   // rows t: [C 16 | g1 64 | g2 64]
-constexpr uint32_t SBO_B2 = 8 * 128, B2_BYTES = 2 * SBO_B2;    // rows n: [B^T 64]
+constexpr uint32_t SBO_BB = 2 * 128, BB_BYTES = 8 * SBO_BB;    // rows s: [B 16]; read K-major (G) and MN-major (D2)
 constexpr uint32_t BC_BYTES = Q * NS * 2;
-constexpr uint32_t TM_D1 = 0, TM_D2 = 64, TM_P = 96, TM_STAGE = 160, TMEM_COLS = 512;
+constexpr uint32_t TM_D1 = 0, TM_D2 = 64, TM_P = 96, TM_G = 160, TM_STAGE = 224, TMEM_COLS = 512;
 constexpr float kRMax = 1.0e24f;  // ~2^80
 constexpr float kNegLog2e = -1.4426950408889634f;
-// nanoseconds between polls for the roles that have slack (producer, builders, the epilogue warps'
-// first wait of a tile); the gate warps and the MMA issuer poll without sleeping
-constexpr int kRelaxProd = 100, kRelaxBuild = 100, kRelaxEpi = 64;
-constexpr int EPI_A_COLS = 16;    // columns of a tile the carry warps take in the epilogue (rest: warps 4-7)
+// nanoseconds between polls for the roles that have slack; the main warps and the MMA issuer poll
+// without sleeping
+#ifndef RLX_P
+#define RLX_P 1000
+#define RLX_B 400
+#define RLX_C 200
+#define RLX_S 500
+#endif
+constexpr int kRelaxProd = RLX_P, kRelaxBuild = RLX_B, kRelaxCarry = RLX_C, kRelaxStore = RLX_S;
+#ifndef PRE_B
+#define PRE_B 0
+#define PRE_C 0
+#define PRE_S 0
+#endif
 
 __device__ __forceinline__ float fast_ex2(float x) {
   float r;
@@ -81,32 +98,6 @@ __device__ __forceinline__ float fast_rcp(float x) {
   return r;
 }
 
-#ifdef NAJU_PROF
-__device__ unsigned long long g_prof[48];
-#define PROF_MARK(i)                                                      \
-  do {                                                                    \
-    if ((threadIdx.x & 127) == 0) {                                       \
-      const long long now_ = clock64();                                   \
-      atomicAdd(&g_prof[i], static_cast<unsigned long long>(now_ - pt_)); \
-      pt_ = now_;                                                         \
-    }                                                                     \
-  } while (0)
-#define PROF_INIT long long pt_ = clock64()
-// same for the single-warp roles (lane 0 marks)
-#define PROF_MARK1(i)                                                     \
-  do {                                                                    \
-    if ((threadIdx.x & 31) == 0) {                                        \
-      const long long now_ = clock64();                                   \
-      atomicAdd(&g_prof[i], static_cast<unsigned long long>(now_ - pt_)); \
-      pt_ = now_;                                                         \
-    }                                                                     \
-  } while (0)
-#else
-#define PROF_MARK1(i) do {} while (0)
-#define PROF_MARK(i) do {} while (0)
-#define PROF_INIT do {} while (0)
-#endif
-
 struct Maps {
   CUtensorMap u, fl, il, bm, cm, y;
 };
@@ -114,31 +105,55 @@ struct Maps {
 template <typename TG>
 struct Smem {
   static constexpr uint32_t slab_bytes = SLAB * kDT * (2 + 2 * sizeof(TG));  // u, f_logit, i_logit
-  // With 16-bit logits there is room to keep a second copy of the tile's u for the epilogue
-  // (D_skip u_t); with fp32 logits the epilogue reads u from global memory instead.
-  static constexpr bool kStashU = sizeof(TG) == 2;
+  // Input slabs are requested as far ahead as the ring is deep, and a slab is on its way for a
+  // microsecond or more: with 16-bit logits the ring holds 7 slabs (1.75 tiles), with fp32 logits
+  // (larger slabs) 4.
+  static constexpr int RING = sizeof(TG) == 2 ? NAJU_RING16 : 4;
+#ifndef NAJU_NY16
+#define NAJU_NY16 1
+#endif
+  static constexpr int NY = sizeof(TG) == 2 ? NAJU_NY16 : 1;   // output staging tiles
   static constexpr uint32_t off_ring = 0;
-  static constexpr uint32_t off_U = off_ring + RING * slab_bytes;                      // [NSTAGE][Q][128]
-  static constexpr uint32_t off_AW = off_U + (kStashU ? NSTAGE * Q * kDT * 2 : 0);     // [NSTAGE]
-  static constexpr uint32_t off_AH = off_AW + NSTAGE * AW_BYTES;
-  static constexpr uint32_t off_B1 = off_AH + AH_BYTES;             // [NSTAGE]
-  static constexpr uint32_t off_B2 = off_B1 + NSTAGE * B1_BYTES;    // [NSTAGE]
-  static constexpr uint32_t off_bc = off_B2 + NSTAGE * B2_BYTES;    // [2 tiles][B raw | C raw]
-  static constexpr uint32_t total = off_bc + 2 * 2 * BC_BYTES;
+  static constexpr uint32_t off_Y = off_ring + RING * slab_bytes;    // [NY][Q][128]
+  // The builders' MMA addresses the 64 C rows of a stage as a 128-row operand: the 18 KB after a
+  // stage's B1 buffer must be readable shared memory, so the large operand-row buffers come last.
+  static constexpr uint32_t off_B1 = off_Y + NY * Q * kDT * 2;       // [NSTAGE]
+  static constexpr uint32_t off_BB = off_B1 + NSTAGE * B1_BYTES;     // [NSTAGE]
+  static constexpr uint32_t off_bc = off_BB + NSTAGE * BB_BYTES;     // [2 tiles][B raw | C raw]
+  static constexpr uint32_t off_AH = off_bc + 2 * 2 * BC_BYTES;
+  static constexpr uint32_t off_AW = off_AH + AH_BYTES;              // [NSTAGE]
+  static constexpr uint32_t total = off_AW + NSTAGE * AW_BYTES;
+  static_assert(off_B1 + (NSTAGE + 1) * B1_BYTES <= total, "the 128-row view of a stage's C rows stays inside shared memory");
 };
 
 struct Bars {
-  unsigned long long full[RING], empty[RING];   // input slabs (producer -> gate warps)
-  unsigned long long u_full[NSTAGE];            // the epilogue's copy of the tile's u has landed
+  unsigned long long full[RING_MAX], empty[RING_MAX];   // input slabs (producer <-> the group that owns the slab)
   unsigned long long bc_full[2], bc_empty[2];   // raw B/C rows per tile parity
+  unsigned long long lprod[NSTAGE][NGRP];       // a group's retention products are published
   unsigned long long part[NSTAGE][NSLAB];       // operand-row chunks of one slab written (128 threads)
-  unsigned long long a_full[NSTAGE];            // all gate threads done with the tile (P_t in TMEM, flags)
+  unsigned long long g_full[NSTAGE];            // the builders' own MMA (G = C B^T) is complete
   unsigned long long ops_full[NSTAGE];          // builder -> MMA issuer
-  unsigned long long d2_full[NSTAGE];           // D2 and the first part of D1 complete
+  unsigned long long d2_full[NSTAGE];           // D2 and the time-contraction part of D1 complete
   unsigned long long h_ready;                   // carry warps -> MMA issuer (carry-in row written)
   unsigned long long d1_full[NSTAGE];           // D1 complete (and the stage's shared operands read)
-  unsigned long long stage_free[NSTAGE];        // carry/epilogue warps -> everyone upstream
+  unsigned long long y_staged[NSTAGE];          // main warps: outputs staged, accumulators read -> store warp, MMA issuer
+  unsigned long long acc_free[NSTAGE];          // carry warps: D2 and the tile's flags read -> MMA issuer, last group
+  unsigned long long stage_free[NSTAGE];        // store warp: staging tile read by the store -> epilogue two tiles on
 };
+
+// packed fp32 pairs (one instruction for two lanes of arithmetic)
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
+// Two-term bf16 split of a pair: v ~= hi + lo, both truncations (see split_bf16x2); packed subtraction.
+__device__ __forceinline__ void split_pair(float2 v, uint32_t& hi, uint32_t& lo) {
+  const uint32_t ua = __float_as_uint(v.x), ub = __float_as_uint(v.y);
+  hi = __byte_perm(ua, ub, 0x7632);
+  const float2 h = make_float2(__uint_as_float(ua & 0xFFFF0000u), __uint_as_float(ub & 0xFFFF0000u));
+  const float2 l = fma2(h, make_float2(-1.f, -1.f), v);
+  lo = __byte_perm(__float_as_uint(l.x), __float_as_uint(l.y), 0x7632);
+}
 
 // Exact recurrence of one tile straight from global memory (deep-gate tiles only), run by the 128
 // carry threads from the carry they hold: hw / Pw = state and cumulative decay entering the chunk,
@@ -191,32 +206,41 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ Bars bars;
   __shared__ int s_stage_deep[NSTAGE];
+  __shared__ int s_store_deep[NSTAGE];       // the same flag, handed to the store warp with the staged tile
   __shared__ unsigned int s_tmem;
+  __shared__ float s_L[NSTAGE][NGRP][kDT];   // retention product of a group's 16 steps (as 1/prod f)
+  __shared__ float s_Rend[NSTAGE][kDT];      // 1 / (retention product of the whole chunk)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t sbase = smem_u32(smem);
   const int nchunks = p.nchunks, ctiles = p.B * p.ndt;
   const int x_first = static_cast<int>(blockIdx.x), x_step = static_cast<int>(gridDim.x);
+  // (channel tile, chunk) pairs this CTA walks
+  const int ntotal = (x_first < ctiles ? (ctiles - x_first + x_step - 1) / x_step : 0) * nchunks;
 
   if (tid == 0) {
-    for (int i = 0; i < RING; ++i) {
+    for (int i = 0; i < RING_MAX; ++i) {
       mbar_init(smem_u32(&bars.full[i]), 1);
-      mbar_init(smem_u32(&bars.empty[i]), NGATE);
+      mbar_init(smem_u32(&bars.empty[i]), NHALF / 32);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars.bc_full[i]), 1);
-      mbar_init(smem_u32(&bars.bc_empty[i]), NBUILD);
+      mbar_init(smem_u32(&bars.bc_empty[i]), 1);
     }
     for (int i = 0; i < NSTAGE; ++i) {
-      for (int k = 0; k < NSLAB; ++k) mbar_init(smem_u32(&bars.part[i][k]), NHALF);
-      mbar_init(smem_u32(&bars.a_full[i]), NGATE);
-      mbar_init(smem_u32(&bars.u_full[i]), 1);
+      for (int k = 0; k < NSLAB; ++k) {
+        mbar_init(smem_u32(&bars.part[i][k]), NHALF / 32);     // (arrival counts are in warps)
+        mbar_init(smem_u32(&bars.lprod[i][k]), NHALF / 32);
+      }
       mbar_init(smem_u32(&bars.ops_full[i]), NBUILD);
+      mbar_init(smem_u32(&bars.g_full[i]), 1);
       mbar_init(smem_u32(&bars.d2_full[i]), 1);
-      mbar_init(smem_u32(&bars.stage_free[i]), NEPI);
+      mbar_init(smem_u32(&bars.d1_full[i]), 1);
+      mbar_init(smem_u32(&bars.y_staged[i]), NMAIN / 32);
+      mbar_init(smem_u32(&bars.acc_free[i]), NCARRY / 32);
+      mbar_init(smem_u32(&bars.stage_free[i]), 1);   // (indexed by staging tile)
     }
-    mbar_init(smem_u32(&bars.h_ready), NHALF);
-    for (int i = 0; i < NSTAGE; ++i) mbar_init(smem_u32(&bars.d1_full[i]), 1);
+    mbar_init(smem_u32(&bars.h_ready), NCARRY / 32);
     mbar_init_fence();
     if (blockIdx.x == 0) {
       atomicOr(p.fwd_form, 1);  // tell the backward how the forward ran
@@ -225,7 +249,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
   }
   if (warp == 0) tmem_alloc(smem_u32(&s_tmem), TMEM_COLS);
   // the upper triangle of g1/g2 is never written again: clear the shared operands once
-  for (uint32_t i = tid * 16; i < NSTAGE * (B1_BYTES + B2_BYTES); i += NTHREADS * 16)
+  for (uint32_t i = tid * 16; i < NSTAGE * (B1_BYTES + BB_BYTES); i += NTHREADS * 16)
     *reinterpret_cast<uint4*>(smem + SM::off_B1 + i) = make_uint4(0, 0, 0, 0);
   fence_async_smem();
   tc_fence_before();
@@ -239,27 +263,10 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     if (lane == 0) {
       uint32_t slab = 0;
       int it = 0;
-      // The epilogue's copy of tile j's u goes to the stage buffer once the tile two back has left
-      // it; it is requested one tile late, where waiting for that cannot hold up any other load.
-      int pb = 0, pd0 = 0, pt0 = 0;
-      auto load_u_copy = [&](int j) {
-        if constexpr (SM::kStashU) {
-          const int st = j & 1;
-          if (j >= NSTAGE && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.stage_free[st]), ((j >> 1) & 1) ^ 1)) timeout();
-          const uint32_t bar = smem_u32(&bars.u_full[st]);
-          mbar_arrive_expect_tx(bar, Q * kDT * 2);
-          for (int k = 0; k < NSLAB; ++k)
-            tma_load_3d(sbase + SM::off_U + st * Q * kDT * 2 + k * SLAB * kDT * 2, &maps.u, pd0, pt0 + k * SLAB, pb, bar);
-        }
-      };
       for (int x = x_first; x < ctiles; x += x_step) {
         const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
         for (int c = 0; c < nchunks; ++c, ++it) {
           const int t0 = c * Q;
-          if (it >= 1) load_u_copy(it - 1);
-          pb = b;
-          pd0 = d0;
-          pt0 = t0;
           if (it >= 2 && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.bc_empty[it & 1]), ((it >> 1) & 1) ^ 1)) timeout();
           {
             const uint32_t bar = smem_u32(&bars.bc_full[it & 1]);
@@ -269,8 +276,8 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
             tma_load_3d(dst + BC_BYTES, &maps.cm, 0, t0, b, bar);
           }
           for (int k = 0; k < NSLAB; ++k, ++slab) {
-            const uint32_t slot = slab % RING, ph = (slab / RING) & 1;
-            if (slab >= RING && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
+            const uint32_t slot = slab % SM::RING, ph = (slab / SM::RING) & 1;
+            if (slab >= SM::RING && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
             const uint32_t bar = smem_u32(&bars.full[slot]);
             const uint32_t dst = sbase + SM::off_ring + slot * SM::slab_bytes;
             mbar_arrive_expect_tx(bar, SM::slab_bytes);
@@ -280,72 +287,76 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
         }
       }
-      if (it >= 1) load_u_copy(it - 1);
     }
   } else if (warp >= W_BUILD && warp < W_BUILD + NBUILD) {
     // ===================================================================== operand builders
-    const int g = lane >> 2, t4 = lane & 3;
     const int bw = warp - W_BUILD, blane = bw * 32 + lane;
-    int it = 0;
-    PROF_INIT;
-    for (int x = x_first; x < ctiles; x += x_step) {
-      for (int c = 0; c < nchunks; ++c, ++it) {
-        const int st = it & 1;
-        if (!mbar_wait_relaxed<kRelaxBuild>(smem_u32(&bars.bc_full[st]), (it >> 1) & 1)) timeout();
-        // stage st: the MMAs of the tile two back must have read B1 / B2 (its epilogue may still run)
-        if (it >= NSTAGE && !mbar_wait_relaxed<kRelaxBuild>(smem_u32(&bars.d1_full[st]), ((it >> 1) & 1) ^ 1)) timeout();
-        PROF_MARK1(40);
-        unsigned char* s_B1 = smem + SM::off_B1 + st * B1_BYTES;
-        unsigned char* s_B2 = smem + SM::off_B2 + st * B2_BYTES;
-        const __nv_bfloat16* Braw = reinterpret_cast<const __nv_bfloat16*>(smem + SM::off_bc + st * 2 * BC_BYTES);
-        const __nv_bfloat16* Craw = Braw + Q * NS;
-        for (int e = blane; e < Q * 2; e += 32 * NBUILD) {  // C columns of B1: 32 bytes per row
-          const int t = e >> 1, half = e & 1;
-          *reinterpret_cast<uint4*>(s_B1 + op_off16(t, B1_C * 8 + half * 8, SBO_B1)) =
-              *reinterpret_cast<const uint4*>(Craw + t * NS + half * 8);
-        }
-        for (int e = blane; e < NS * (Q / 8); e += 32 * NBUILD) {  // B2 = B^T: (row n, eight columns s) per store
-          const int n = e % NS, s8 = e / NS;
-          uint32_t w[4];
+    const int t = blane;                           // the accumulator row (step) this thread reads back
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t idG = umma_idesc(128, Q, 1);
+    for (int it = 0; it < ntotal; ++it) {
+      const int st = it & 1;
+      const uint32_t par = (it >> 1) & 1;
+      if (!mbar_wait_relaxed<kRelaxBuild>(smem_u32(&bars.bc_full[st]), par)) timeout();
+      // stage st: the MMAs of the tile two back must have read B1 / BB (its epilogue may still run)
+      if (it >= NSTAGE && !mbar_wait_presleep<PRE_B, kRelaxBuild>(smem_u32(&bars.d1_full[st]), par ^ 1)) timeout();
+      unsigned char* s_B1 = smem + SM::off_B1 + st * B1_BYTES;
+      unsigned char* s_BB = smem + SM::off_BB + st * BB_BYTES;
+      const __nv_bfloat16* Braw = reinterpret_cast<const __nv_bfloat16*>(smem + SM::off_bc + st * 2 * BC_BYTES);
+      const __nv_bfloat16* Craw = Braw + Q * NS;
+      // the chunk's C and B rows in operand layout: 32 bytes per row, two 16-byte pieces
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t lo = *reinterpret_cast<const unsigned short*>(Braw + (8 * s8 + 2 * j) * NS + n);
-            const uint32_t hi = *reinterpret_cast<const unsigned short*>(Braw + (8 * s8 + 2 * j + 1) * NS + n);
-            w[j] = lo | (hi << 16);
-          }
-          *reinterpret_cast<uint4*>(s_B2 + op_off16(n, 8 * s8, SBO_B2)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-#pragma unroll 1
-        for (int mt = 0; mt < Q / 16; ++mt) {  // G = tril(C B^T) in two bf16 terms
-          const int r0 = 16 * mt + g, r1 = r0 + 8;
-          const uint32_t a0 = *reinterpret_cast<const uint32_t*>(Craw + r0 * NS + 2 * t4);
-          const uint32_t a1 = *reinterpret_cast<const uint32_t*>(Craw + r1 * NS + 2 * t4);
-          const uint32_t a2 = *reinterpret_cast<const uint32_t*>(Craw + r0 * NS + 2 * t4 + 8);
-          const uint32_t a3 = *reinterpret_cast<const uint32_t*>(Craw + r1 * NS + 2 * t4 + 8);
-          for (int nt = 0; nt <= 2 * mt + 1; ++nt) {
-            if (((mt * (mt + 1) + nt) % NBUILD) != bw) continue;  // 16x8 blocks dealt round-robin to the builder warps
-            float c4[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Braw + (8 * nt + g) * NS + 2 * t4);
-            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Braw + (8 * nt + g) * NS + 2 * t4 + 8);
-            mma_bf16_16x8x16(c4, a0, a1, a2, a3, b0, b1);
-            const int s0 = 8 * nt + 2 * t4;
-            uint32_t hi, lo;
-            split_bf16x2(s0 <= r0 ? c4[0] : 0.f, s0 + 1 <= r0 ? c4[1] : 0.f, hi, lo);
-            *reinterpret_cast<uint32_t*>(s_B1 + op_off16(r0, B1_G1 * 8 + s0, SBO_B1)) = hi;
-            *reinterpret_cast<uint32_t*>(s_B1 + op_off16(r0, B1_G2 * 8 + s0, SBO_B1)) = lo;
-            split_bf16x2(s0 <= r1 ? c4[2] : 0.f, s0 + 1 <= r1 ? c4[3] : 0.f, hi, lo);
-            *reinterpret_cast<uint32_t*>(s_B1 + op_off16(r1, B1_G1 * 8 + s0, SBO_B1)) = hi;
-            *reinterpret_cast<uint32_t*>(s_B1 + op_off16(r1, B1_G2 * 8 + s0, SBO_B1)) = lo;
-          }
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(smem_u32(&bars.ops_full[st]));
-          mbar_arrive(smem_u32(&bars.bc_empty[st]));
-        }
-        PROF_MARK1(41);
+      for (int half = 0; half < 2; ++half) {
+        *reinterpret_cast<uint4*>(s_B1 + op_off16(t, B1_C * 8 + half * 8, SBO_B1)) =
+            *reinterpret_cast<const uint4*>(Craw + t * NS + half * 8);
+        *reinterpret_cast<uint4*>(s_BB + op_off16(t, half * 8, SBO_BB)) =
+            *reinterpret_cast<const uint4*>(Braw + t * NS + half * 8);
       }
+      fence_async_smem();
+      tc_fence_before();
+      bar_sync<3, 32 * NBUILD>();                  // both warps: rows written, last tile's G read
+      tc_fence_after();
+      if (blane == 0) {
+        mbar_arrive(smem_u32(&bars.bc_empty[st]));  // the raw rows have been read
+        // G[t, s] = <C_t, B_s>: M = 128 rows of which the 64 steps are real (the rest of the A
+        // operand is whatever follows the C rows in shared memory; those accumulator rows are
+        // never read), N = 64, K = 16 states
+        umma_bf16(tmem + st * TM_STAGE + TM_G, umma_desc(sbase + SM::off_B1 + st * B1_BYTES + B1_C * 128, 128, SBO_B1),
+                  umma_desc(sbase + SM::off_BB + st * BB_BYTES, 128, SBO_BB), idG, 0u);
+        umma_commit(smem_u32(&bars.g_full[st]));
+      }
+      if (!mbar_wait(smem_u32(&bars.g_full[st]), par)) timeout();
+      tc_fence_after();
+      // row t of tril(G) in two bf16 terms -> [g1 | g2] of row t; chunks right of the diagonal stay
+      // zero (cleared once, never written)
+      unsigned char* row = s_B1 + static_cast<uint32_t>(t >> 3) * SBO_B1 + static_cast<uint32_t>(t & 7) * 16;
+      const uint32_t tG = tmem + st * TM_STAGE + TM_G + lane_off;
+      const int nch16 = 2 * (bw + 1);              // 16-column pieces up to this warp's last diagonal
+#pragma unroll 1
+      for (int c16 = 0; c16 < nch16; ++c16) {
+        uint32_t x[16];
+        tmem_ld16_async(tG + 16 * c16, x);
+        tmem_ld_wait16(x);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int c8 = 2 * c16 + h;
+          if (c8 <= (t >> 3)) {
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int s = 8 * c8 + 2 * k;
+              split_pair(make_float2(s <= t ? __uint_as_float(x[8 * h + 2 * k]) : 0.f,
+                                     s + 1 <= t ? __uint_as_float(x[8 * h + 2 * k + 1]) : 0.f), hi[k], lo[k]);
+            }
+            *reinterpret_cast<uint4*>(row + (B1_G1 + c8) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(row + (B1_G2 + c8) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          }
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars.ops_full[st]));
     }
   } else if (warp == W_MMA) {
     // ===================================================================== MMA issuer
@@ -353,164 +364,83 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       const uint32_t id16 = umma_idesc(128, NS, 1), id64 = umma_idesc(128, Q, 1);
       // operand addresses are fixed: build the descriptors once, offset the address field per use
       const uint64_t dAW0 = umma_desc(sbase + SM::off_AW, 128, SBO_AW), dAH = umma_desc(sbase + SM::off_AH, 128, SBO_AH);
-      const uint64_t dB10 = umma_desc(sbase + SM::off_B1, 128, SBO_B1), dB20 = umma_desc(sbase + SM::off_B2, 128, SBO_B2);
+      const uint64_t dB10 = umma_desc(sbase + SM::off_B1, 128, SBO_B1);
+      // the B rows read MN-major (N = state contiguous, K = step): LBO = bytes between 8-step groups,
+      // SBO = bytes between 8-state chunks
+      const uint64_t dBB0 = umma_desc(sbase + SM::off_BB, SBO_BB, 128);
+      const uint32_t id16m = id16 | (1u << 16);
       auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
-      PROF_INIT;
+      for (int it = 0; it < ntotal; ++it) {
+        const int st = it & 1;
+        const uint32_t par = (it >> 1) & 1;
+        const uint64_t dAW = dAW0 + off(st * AW_BYTES), dB1 = dB10 + off(st * B1_BYTES), dBB = dBB0 + off(st * BB_BYTES);
+        const uint32_t tst = tmem + st * TM_STAGE;
+        if (!mbar_wait(smem_u32(&bars.ops_full[st]), par)) timeout();
+        // the stage's accumulators: every reader of the tile two back is done with them
+        if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.y_staged[st]), par ^ 1)) timeout();
+        if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.acc_free[st]), par ^ 1)) timeout();
+#pragma unroll 1
+        for (int ks = 0; ks < NSLAB; ++ks) {
+          // the time contractions of slab ks run while the other groups are still on their slabs
+          if (!mbar_wait(smem_u32(&bars.part[st][ks]), par)) timeout();
+          tc_fence_after();
+          const uint64_t w1 = dAW + off((AW_W1 + 2 * ks) * 128), w2 = dAW + off((AW_W2 + 2 * ks) * 128);
+          umma_bf16(tst + TM_D2, w1, dBB + off(2 * ks * SBO_BB), id16m, ks > 0);   // D2 += (w1 + w2) . B^T
+          umma_bf16(tst + TM_D2, w2, dBB + off(2 * ks * SBO_BB), id16m, 1u);
+          umma_bf16(tst + TM_D1, w1, dB1 + off((B1_G1 + 2 * ks) * 128), id64, ks > 0);  // D1 += w1.g1 + w1.g2 + w2.g1
+          umma_bf16(tst + TM_D1, w1, dB1 + off((B1_G2 + 2 * ks) * 128), id64, 1u);
+          umma_bf16(tst + TM_D1, w2, dB1 + off((B1_G1 + 2 * ks) * 128), id64, 1u);
+        }
+        // all four slabs are in: D2 is complete when these MMAs are
+        umma_commit(smem_u32(&bars.d2_full[st]));
+        // (the accumulators of a deep-gate tile are junk and are simply never read; the carry-in MMAs
+        // run for it all the same, which keeps the barrier phases aligned)
+        if (!mbar_wait(smem_u32(&bars.h_ready), it & 1)) timeout();
+        tc_fence_after();
+        umma_bf16(tst + TM_D1, dAH + off(AH_H1 * 128), dB1 + off(B1_C * 128), id64, 1u);  // D1 += (h1 + h2) . C
+        umma_bf16(tst + TM_D1, dAH + off(AH_H2 * 128), dB1 + off(B1_C * 128), id64, 1u);
+        umma_commit(smem_u32(&bars.d1_full[st]));
+      }
+    }
+  } else if (warp == W_STORE) {
+    // ===================================================================== store warp
+    if (lane == 0) {
       int it = 0;
       for (int x = x_first; x < ctiles; x += x_step) {
+        const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
         for (int c = 0; c < nchunks; ++c, ++it) {
           const int st = it & 1;
-          const uint32_t par = (it >> 1) & 1;
-          const uint64_t dAW = dAW0 + off(st * AW_BYTES), dB1 = dB10 + off(st * B1_BYTES), dB2 = dB20 + off(st * B2_BYTES);
-          const uint32_t tst = tmem + st * TM_STAGE;
-          if (!mbar_wait(smem_u32(&bars.ops_full[st]), par)) timeout();
-          PROF_MARK1(32);
-#pragma unroll 1
-          for (int ks = 0; ks < NSLAB; ++ks) {
-            // the time contractions of slab ks run while the gate warps are still on the other slabs
-            if (!mbar_wait(smem_u32(&bars.part[st][ks]), par)) timeout();
-            tc_fence_after();
-            const uint64_t w1 = dAW + off((AW_W1 + 2 * ks) * 128), w2 = dAW + off((AW_W2 + 2 * ks) * 128);
-            umma_bf16(tst + TM_D2, w1, dB2 + off(2 * ks * 128), id16, ks > 0);   // D2 += (w1 + w2) . B^T
-            umma_bf16(tst + TM_D2, w2, dB2 + off(2 * ks * 128), id16, 1u);
-            umma_bf16(tst + TM_D1, w1, dB1 + off((B1_G1 + 2 * ks) * 128), id64, ks > 0);  // D1 += w1.g1 + w1.g2 + w2.g1
-            umma_bf16(tst + TM_D1, w1, dB1 + off((B1_G2 + 2 * ks) * 128), id64, 1u);
-            umma_bf16(tst + TM_D1, w2, dB1 + off((B1_G1 + 2 * ks) * 128), id64, 1u);
+          if (!mbar_wait_presleep<PRE_S, kRelaxStore>(smem_u32(&bars.y_staged[st]), (it >> 1) & 1)) timeout();
+          if (!s_store_deep[st]) {
+            // the staged tile leaves by TMA (steps past T and channels past D are clipped); the stage
+            // is released once the store has read it
+            tma_store_3d(&maps.y, d0, c * Q, b, sbase + SM::off_Y + (it % SM::NY) * Q * kDT * 2);
+            tma_store_commit();
+            tma_store_wait_read();
           }
-          // a deep-gate tile is decided only now (all gate threads done): its accumulators are junk
-          // and are simply not read; one carry-in phase per tile keeps the phase counts aligned
-          PROF_MARK1(33);
-          if (!mbar_wait(smem_u32(&bars.a_full[st]), par)) timeout();
-          umma_commit(smem_u32(&bars.d2_full[st]));
-          PROF_MARK1(34);
-          if (!mbar_wait(smem_u32(&bars.h_ready), it & 1)) timeout();
-          PROF_MARK1(35);
-          if (!s_stage_deep[st]) {
-            tc_fence_after();
-            umma_bf16(tst + TM_D1, dAH + off(AH_H1 * 128), dB1 + off(B1_C * 128), id64, 1u);  // D1 += (h1 + h2) . C
-            umma_bf16(tst + TM_D1, dAH + off(AH_H2 * 128), dB1 + off(B1_C * 128), id64, 1u);
-          }
-          umma_commit(smem_u32(&bars.d1_full[st]));
-          PROF_MARK1(36);
+          mbar_arrive(smem_u32(&bars.stage_free[it % SM::NY]));
         }
       }
+      tma_store_wait_all();
     }
-  } else if (warp >= 8) {
-    // ===================================================================== gate warps
-    const int half = (warp - 8) >> 2;      // gate group: which slabs of every chunk this thread evaluates
-    const int q = tid & (kDT - 1);         // channel within the tile
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    uint32_t slab = 0;
-    int it = 0;
-    PROF_INIT;
-    for (int x = x_first; x < ctiles; x += x_step) {
-      for (int c = 0; c < nchunks; ++c, ++it) {
-        const int st = it & 1;
-        if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.stage_free[st]), ((it >> 1) & 1) ^ 1)) timeout();
-        PROF_MARK(16 + 8 * half);
-        tc_fence_after();
-        unsigned char* a_row = smem + SM::off_AW + st * AW_BYTES + static_cast<uint32_t>(q >> 3) * SBO_AW +
-                               static_cast<uint32_t>(q & 7) * 16;
-        const uint32_t tP = tmem + st * TM_STAGE + TM_P + lane_off;
-        // Steps past the end of the sequence (last chunk only) arrive as zeros from TMA: u = 0 keeps
-        // them out of every sum, and the carry warps take the decay product at the last real step.
-        float R = 1.f;
-#pragma unroll 1
-        for (int k = 0; k < NSLAB; ++k) {
-          const uint32_t sidx = slab + k, slot = sidx % RING, ph = (sidx / RING) & 1;
-          const bool mine = (k / SPG) == half;
-          // (every thread waits for the slab before releasing it, needed or not: an arrival must
-          // not reach the empty barrier before its previous phase has completed)
-#ifdef NAJU_PROF
-          const long long tw_ = clock64();
-#endif
-          if (!mbar_wait(smem_u32(&bars.full[slot]), ph)) timeout();
-#ifdef NAJU_PROF
-          if ((threadIdx.x & 127) == 0) atomicAdd(&g_prof[16 + 8 * half + 3], static_cast<unsigned long long>(clock64() - tw_));
-#endif
-          const unsigned char* sl = smem + SM::off_ring + slot * SM::slab_bytes;
-          const TA* s_u = reinterpret_cast<const TA*>(sl) + q;
-          const TG* s_fl = reinterpret_cast<const TG*>(sl + SLAB * kDT * 2) + q;
-          const TG* s_il = s_fl + SLAB * kDT;
-          if (!mine) {
-            if (k / SPG < half) {
-              // slabs before this group's: retention products only.  The sixteen factors are
-              // independent: multiply them as a tree, not as a chain.
-              float fac[SLAB];
-#pragma unroll
-              for (int tl = 0; tl < SLAB; ++tl) fac[tl] = 1.f + fast_ex2(ld_as_f32(s_fl, tl * kDT) * kNegLog2e);
-#pragma unroll
-              for (int w = SLAB / 2; w >= 1; w >>= 1)
-#pragma unroll
-                for (int i = 0; i < w; ++i) fac[i] *= fac[i + w];
-              R *= fac[0];
-            }
-            mbar_arrive(smem_u32(&bars.empty[slot]));
-            continue;
-          }
-#pragma unroll 1
-          for (int j8 = 0; j8 < SLAB / 8; ++j8) {  // (loops are kept rolled: five roles share the instruction cache)
-            float wv[8];
-            uint32_t pv[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int tl = 8 * j8 + j;
-              const float flv = ld_as_f32(s_fl, tl * kDT);
-              const float ilv = fmaxf(ld_as_f32(s_il, tl * kDT), -30.f);
-              const float uv = ld_as_f32(s_u, tl * kDT);
-              const float a = fast_ex2(flv * kNegLog2e);
-              const float opb = 1.f + fast_ex2(ilv * kNegLog2e);  // 1/i
-              R *= 1.f + a;
-              const float r = fast_rcp(R * opb);
-              pv[j] = __float_as_uint(opb * r);                   // P_t = 1/R_t
-              wv[j] = uv * (R * r) * R;                           // u * i * R
-            }
-            uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-            split_bf16x2(wv[0], wv[1], h0, l0);
-            split_bf16x2(wv[2], wv[3], h1, l1);
-            split_bf16x2(wv[4], wv[5], h2, l2);
-            split_bf16x2(wv[6], wv[7], h3, l3);
-            const int ch = k * (SLAB / 8) + j8;
-            *reinterpret_cast<uint4*>(a_row + (AW_W1 + ch) * 128) = make_uint4(h0, h1, h2, h3);
-            *reinterpret_cast<uint4*>(a_row + (AW_W2 + ch) * 128) = make_uint4(l0, l1, l2, l3);
-            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(tP + 8 * ch),
-                         "r"(pv[0]), "r"(pv[1]), "r"(pv[2]), "r"(pv[3]), "r"(pv[4]), "r"(pv[5]), "r"(pv[6]), "r"(pv[7])
-                         : "memory");
-          }
-          mbar_arrive(smem_u32(&bars.empty[slot]));
-          fence_async_smem();
-          mbar_arrive(smem_u32(&bars.part[st][k]));
-        }
-        slab += NSLAB;
-        PROF_MARK(16 + 8 * half + 1);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        const bool deep = half == NGRP - 1 && !(R < kRMax);  // the last group holds the whole chunk's product
-        const bool any_deep = bar_or<2, NGATE>(deep);
-        if (tid == 8 * 32) s_stage_deep[st] = any_deep ? 1 : 0;
-        tc_fence_before();
-        mbar_arrive(smem_u32(&bars.a_full[st]));
-        PROF_MARK(16 + 8 * half + 2);
-      }
-    }
-  } else {
-    // ===================================================================== carry / epilogue warps
-    const int half = warp >> 2;           // 0: carry + first EPI_A_COLS columns, 1: the other columns
-    const int q = tid & (kDT - 1);
+  } else if (warp >= W_CARRY) {
+    // ===================================================================== carry warps
+    const int q = tid - W_CARRY * 32;     // channel within the tile
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     unsigned char* h_row = smem + SM::off_AH + static_cast<uint32_t>(q >> 3) * SBO_AH + static_cast<uint32_t>(q & 7) * 16;
     auto write_h_row = [&](const float (&hv)[NS]) {
       uint32_t hi[8], lo[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) split_bf16x2(hv[2 * k], hv[2 * k + 1], hi[k], lo[k]);
+      for (int k = 0; k < 8; ++k) split_pair(make_float2(hv[2 * k], hv[2 * k + 1]), hi[k], lo[k]);
       *reinterpret_cast<uint4*>(h_row + (AH_H1 + 0) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       *reinterpret_cast<uint4*>(h_row + (AH_H1 + 1) * 128) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
       *reinterpret_cast<uint4*>(h_row + (AH_H2 + 0) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       *reinterpret_cast<uint4*>(h_row + (AH_H2 + 1) * 128) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(smem_u32(&bars.h_ready));
+      mbar_arrive_warp(smem_u32(&bars.h_ready));
     };
-    // state / cumulative decay entering the current chunk (first half only)
+    // state / cumulative decay entering the current chunk
     float hc[NS];
     float Pc = 1.f;
     auto load_h0 = [&](int x) {  // carry-in of the first chunk of channel tile x
@@ -521,12 +451,11 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       Pc = 1.f;
     };
     // One carry-in row (one h_ready phase) is posted per tile, one tile ahead.
-    if (half == 0 && x_first < ctiles) {
+    if (x_first < ctiles) {
       load_h0(x_first);
       write_h_row(hc);
     }
     int it = 0;
-    PROF_INIT;
     for (int x = x_first; x < ctiles; x += x_step) {
       TileCoord tcd;
       tcd.per_chunk = ctiles;
@@ -537,153 +466,232 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       tcd.cols = min(kDT, p.D - tcd.d0);
       tcd.d = tcd.d0 + q;
       tcd.d_ok = tcd.d < p.D;
-      const float Dv = tcd.d_ok ? __ldg(p.Dskip + tcd.d) : 0.f;
       for (int c = 0; c < nchunks; ++c, ++it) {
         const int st = it & 1;
-        if (!mbar_wait_relaxed<kRelaxEpi>(smem_u32(&bars.d2_full[st]), (it >> 1) & 1)) timeout();
-        PROF_MARK(8 * half);
+        if (!mbar_wait_presleep<PRE_C, kRelaxCarry>(smem_u32(&bars.d2_full[st]), (it >> 1) & 1)) timeout();
+        if (!mbar_wait(smem_u32(&bars.part[st][NGRP - 1]), (it >> 1) & 1)) timeout();  // (the writers of s_Rend arrived here)
         tcd.c = c;
         tcd.tile = static_cast<int64_t>(c) * ctiles + x;
         tcd.t0 = c * Q;
         tcd.len = min(Q, p.T - tcd.t0);
-        const int len = tcd.len;
-        const bool deep = s_stage_deep[st] != 0;
+        // 1 / (the chunk's retention product), from the last group; a tile where it overflowed in any
+        // channel (deep gates) cannot use the factorisation
+        const float Rend = s_Rend[st][q];
+        const bool deep = bar_or<2, NCARRY>(!(Rend < kRMax));
+        if (q == 0) s_stage_deep[st] = deep ? 1 : 0;
         tc_fence_after();
-        const uint32_t trow = tmem + st * TM_STAGE + lane_off;
-        if (half == 0) {
-          if (deep) {
-            if (q == 0) atomicOr(p.fwd_form, 2);
-            exact_tile_from_global<TA, TG>(p, tcd, q, hc, Pc);
-          } else {
-            // chunk aggregate from D2: chunk-end state = next carry-in = checkpoint.  The decay
-            // product of the chunk is P at its last real step.
-            uint32_t sr[16], pl[1];
-            tmem_ld16_async(trow + TM_D2, sr);
-            asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(pl[0]) : "r"(trow + TM_P + len - 1) : "memory");
-            tmem_ld_wait16(sr);
-            asm volatile("" : "+r"(pl[0])::"memory");
-            const float P = __uint_as_float(pl[0]);
+        if (deep) {
+          if (q == 0) atomicOr(p.fwd_form, 2);
+          exact_tile_from_global<TA, TG>(p, tcd, q, hc, Pc);
+        } else {
+          // chunk aggregate from D2: chunk-end state = next carry-in = checkpoint
+          uint32_t sr[16];
+          tmem_ld16_async(tmem + st * TM_STAGE + lane_off + TM_D2, sr);
+          tmem_ld_wait16(sr);
+          const float P = __frcp_rn(Rend);
 #pragma unroll
-            for (int n = 0; n < NS; ++n) hc[n] = P * (hc[n] + __uint_as_float(sr[n]));
-            const int64_t slot = tcd.tile * kDT + q;
-            float4* dstS = reinterpret_cast<float4*>(p.ckS + slot * NS);
+          for (int n = 0; n < NS; ++n) hc[n] = P * (hc[n] + __uint_as_float(sr[n]));
+          const int64_t slot = tcd.tile * kDT + q;
+          float4* dstS = reinterpret_cast<float4*>(p.ckS + slot * NS);
 #pragma unroll
-            for (int q4 = 0; q4 < NS / 4; ++q4)
-              dstS[q4] = make_float4(hc[4 * q4], hc[4 * q4 + 1], hc[4 * q4 + 2], hc[4 * q4 + 3]);
-            Pc *= P;
-            p.ckP[slot] = Pc;
-            write_final<NS>(p, tcd, hc, Pc);
-          }
+          for (int q4 = 0; q4 < NS / 4; ++q4)
+            dstS[q4] = make_float4(hc[4 * q4], hc[4 * q4 + 1], hc[4 * q4 + 2], hc[4 * q4 + 3]);
+          Pc *= P;
+          p.ckP[slot] = Pc;
+          write_final<NS>(p, tcd, hc, Pc);
         }
-        PROF_MARK(8 * half + 1);
-        if (!mbar_wait(smem_u32(&bars.d1_full[st]), (it >> 1) & 1)) timeout();
-        PROF_MARK(8 * half + 2);
-        tc_fence_after();
-        if (half == 0) {
-          // the last MMA of this tile has read the carry-in row: post the next tile's row now
-          if (c + 1 < nchunks) {
-            write_h_row(hc);
-          } else if (x + x_step < ctiles) {
-            load_h0(x + x_step);
-            write_h_row(hc);
-          }
-        }
-        PROF_MARK(8 * half + 3);
-        // ---- epilogue: y_t = P_t D1[d][t] + D_skip u_t, staged in the (now dead) operand rows of this
-        // stage (step t -> 256 contiguous bytes), written out with 16-byte stores
-        unsigned char* ystage = smem + SM::off_AW + st * AW_BYTES;
-        if (!deep) {
-          const TA* s_u = reinterpret_cast<const TA*>(smem + SM::off_U + st * Q * kDT * 2) + q;
-          const TA* gu = reinterpret_cast<const TA*>(p.u) + tcd.b * p.u_sb + static_cast<int64_t>(tcd.t0) * p.u_st + tcd.d;
-          if constexpr (SM::kStashU) {
-            if (!mbar_wait(smem_u32(&bars.u_full[st]), (it >> 1) & 1)) timeout();
-          }
-          const int c_lo = half ? EPI_A_COLS : 0;
-          const int nblk = half ? (Q - EPI_A_COLS) / 8 : EPI_A_COLS / 8;
-          uint32_t vA[8], pA[8], vB[8], pB[8];
-          auto emit8 = [&](int col, const uint32_t (&v)[8], const uint32_t (&pt)[8]) {
-            unsigned char* dst = ystage + (col >> 3) * SBO_AW + q * 2;  // (col is a multiple of 8)
-#pragma unroll
-            for (int k = 0; k < 8; k += 2) {
-              const int t = col + k;
-              float y0 = __uint_as_float(pt[k]) * __uint_as_float(v[k]);
-              float y1 = __uint_as_float(pt[k + 1]) * __uint_as_float(v[k + 1]);
-              if (Dv != 0.f) {
-                if constexpr (SM::kStashU) {  // (u past the end of the sequence is zero)
-                  y0 = fmaf(Dv, ld_as_f32(s_u, t * kDT), y0);
-                  y1 = fmaf(Dv, ld_as_f32(s_u, (t + 1) * kDT), y1);
-                } else {
-                  if (t < len) y0 = fmaf(Dv, to_f32(gu[static_cast<int64_t>(t) * p.u_st]), y0);
-                  if (t + 1 < len) y1 = fmaf(Dv, to_f32(gu[static_cast<int64_t>(t + 1) * p.u_st]), y1);
-                }
-              }
-              unsigned short o0, o1;
-              if constexpr (std::is_same<TA, __nv_bfloat16>::value) {
-                const uint32_t pk = pack_bf16x2(y0, y1);  // one conversion for two steps
-                o0 = static_cast<unsigned short>(pk & 0xFFFFu);
-                o1 = static_cast<unsigned short>(pk >> 16);
-              } else {
-                const __half2 pk = __floats2half2_rn(y0, y1);
-                o0 = __half_as_ushort(__low2half(pk));
-                o1 = __half_as_ushort(__high2half(pk));
-              }
-              *reinterpret_cast<unsigned short*>(dst + k * 256) = o0;
-              *reinterpret_cast<unsigned short*>(dst + (k + 1) * 256) = o1;
-            }
-          };
-          tmem_ld8_async(trow + TM_D1 + c_lo, vA);
-          tmem_ld8_async(trow + TM_P + c_lo, pA);
-          tmem_ld_wait8(vA, pA);
-#pragma unroll 1
-          for (int blk = 0; blk < nblk; blk += 2) {  // two eight-column blocks per trip, loads one block ahead
-            const int col = c_lo + 8 * blk;
-            tmem_ld8_async(trow + TM_D1 + col + 8, vB);
-            tmem_ld8_async(trow + TM_P + col + 8, pB);
-            emit8(col, vA, pA);
-            tmem_ld_wait8(vB, pB);
-            if (blk + 2 < nblk) {
-              tmem_ld8_async(trow + TM_D1 + col + 16, vA);
-              tmem_ld8_async(trow + TM_P + col + 16, pA);
-            }
-            emit8(col + 8, vB, pB);
-            if (blk + 2 < nblk) tmem_ld_wait8(vA, pA);
-          }
-        }
-        PROF_MARK(8 * half + 4);
-        fence_async_smem();
+        // D2 and s_Rend have been read, the tile's deep flag is written: one arrival per warp
         tc_fence_before();
-        bar_sync<1, NEPI>();
-        PROF_MARK(8 * half + 5);
-        if (!deep && tid == 0) {
-          // the staged tile leaves by TMA (steps past T and channels past D are clipped); the stage
-          // is released once the store has read it
-          tma_store_3d(&maps.y, tcd.d0, tcd.t0, tcd.b, smem_u32(ystage));
-          tma_store_commit();
-          tma_store_wait_read();
+        mbar_arrive_warp(smem_u32(&bars.acc_free[st]));
+        if (!mbar_wait(smem_u32(&bars.d1_full[st]), (it >> 1) & 1)) timeout();
+        // the last MMA of this tile has read the carry-in row: post the next tile's row now
+        if (c + 1 < nchunks) {
+          write_h_row(hc);
+        } else if (x + x_step < ctiles) {
+          load_h0(x + x_step);
+          write_h_row(hc);
         }
-        mbar_arrive(smem_u32(&bars.stage_free[st]));
-        PROF_MARK(8 * half + 6);
+      }
+    }
+  } else {
+    // ===================================================================== main warps
+    const int grp = warp >> 2;                     // owns steps [16 grp, 16 grp + 16) of every chunk
+    const int q = (warp & 3) * 32 + lane;          // channel within the tile
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const float2 kk = make_float2(kNegLog2e, kNegLog2e), one2 = make_float2(1.f, 1.f);
+    // the tile whose epilogue is pending (it runs one tile late, after the next tile's operand rows)
+    int e_b = 0, e_d0 = 0, e_t0 = 0, e_len = 0, e_it = -1;
+    float e_Dv = 0.f;
+
+    auto epilogue = [&]() {
+      // y_t = P_t D1[d][t] + D_skip u_t for this thread's 16 steps of the pending tile, into the
+      // stage's staging tile (step t -> 256 contiguous bytes); P_t comes back from TMEM
+      const int st = e_it & 1;
+      const uint32_t par = (e_it >> 1) & 1;
+      if (!mbar_wait(smem_u32(&bars.acc_free[st]), par)) timeout();   // (the deep flag's writers arrived here)
+      if (!mbar_wait(smem_u32(&bars.d1_full[st]), par)) timeout();
+      // the staging tile was last used NY tiles back: that store must have read it
+      const int ys = e_it % SM::NY;
+      if (e_it >= SM::NY && !mbar_wait(smem_u32(&bars.stage_free[ys]), ((e_it / SM::NY) & 1) ^ 1)) timeout();
+      tc_fence_after();
+      const bool deep = s_stage_deep[st] != 0;
+      if (tid == 0) s_store_deep[st] = deep ? 1 : 0;
+      if (!deep) {
+        uint32_t v[SLAB], pv[SLAB];
+        const uint32_t tb = tmem + st * TM_STAGE + lane_off + SLAB * grp;
+        tmem_ld16_async(tb + TM_D1, v);
+        tmem_ld16_async(tb + TM_P, pv);
+        unsigned char* dst = smem + SM::off_Y + ys * (Q * kDT * 2) + (SLAB * grp) * (kDT * 2) + q * 2;
+        const TA* gu = reinterpret_cast<const TA*>(p.u) + e_b * p.u_sb + static_cast<int64_t>(e_t0 + SLAB * grp) * p.u_st + e_d0 + q;
+        tmem_ld_wait16(v);
+        tmem_ld_wait16(pv);
+#pragma unroll
+        for (int j2 = 0; j2 < SLAB / 2; ++j2) {
+          float2 y = mul2(make_float2(__uint_as_float(pv[2 * j2]), __uint_as_float(pv[2 * j2 + 1])),
+                          make_float2(__uint_as_float(v[2 * j2]), __uint_as_float(v[2 * j2 + 1])));
+          if (e_Dv != 0.f) {  // (the mixer passes a zero D_skip: naju/mixer.py:120-124)
+            const int t = SLAB * grp + 2 * j2;
+            float u0 = 0.f, u1 = 0.f;
+            if (t < e_len) u0 = to_f32(gu[static_cast<int64_t>(2 * j2) * p.u_st]);
+            if (t + 1 < e_len) u1 = to_f32(gu[static_cast<int64_t>(2 * j2 + 1) * p.u_st]);
+            y = fma2(make_float2(e_Dv, e_Dv), make_float2(u0, u1), y);
+          }
+          unsigned short o0, o1;
+          if constexpr (std::is_same<TA, __nv_bfloat16>::value) {
+            const uint32_t pk = pack_bf16x2(y.x, y.y);  // one conversion for two steps
+            o0 = static_cast<unsigned short>(pk & 0xFFFFu);
+            o1 = static_cast<unsigned short>(pk >> 16);
+          } else {
+            const __half2 pk = __floats2half2_rn(y.x, y.y);
+            o0 = __half_as_ushort(__low2half(pk));
+            o1 = __half_as_ushort(__high2half(pk));
+          }
+          *reinterpret_cast<unsigned short*>(dst + (2 * j2) * (kDT * 2)) = o0;
+          *reinterpret_cast<unsigned short*>(dst + (2 * j2 + 1) * (kDT * 2)) = o1;
+        }
+        fence_async_smem();
+      }
+      tc_fence_before();
+      mbar_arrive_warp(smem_u32(&bars.y_staged[st]));
+    };
+
+    // one trip more than there are tiles: trip `it` writes the operand rows of tile `it` (if there is
+    // one) and then finishes tile `it - 1`
+    int x = x_first, c = 0, b = 0, d0 = 0;
+    float Dv = 0.f;
+#pragma unroll 1
+    for (int it = 0; it <= ntotal; ++it) {
+      if (it < ntotal) {
+        if (c == 0) {
+          b = x / p.ndt;
+          d0 = (x - b * p.ndt) * kDT;
+          Dv = (d0 + q < p.D) ? __ldg(p.Dskip + d0 + q) : 0.f;
+        }
+        const int st = it & 1;
+        const uint32_t par = (it >> 1) & 1;
+        const int t0 = c * Q, len = min(Q, p.T - t0);
+        const uint32_t sidx = static_cast<uint32_t>(it) * NSLAB + grp, slot = sidx % SM::RING, ph = (sidx / SM::RING) & 1;
+        // ---- (1) retention of the own 16 steps: L_j = prod_{i<=j} (1 + e^{-f_logit_i}), as pairs
+        if (!mbar_wait(smem_u32(&bars.full[slot]), ph)) timeout();
+        const unsigned char* sl = smem + SM::off_ring + slot * SM::slab_bytes;
+        const TA* s_u = reinterpret_cast<const TA*>(sl) + q;
+        const TG* s_fl = reinterpret_cast<const TG*>(sl + SLAB * kDT * 2) + q;
+        const TG* s_il = s_fl + SLAB * kDT;
+        float2 L[SLAB / 2];
+        {
+          float2 qv[SLAB / 2];
+#pragma unroll
+          for (int j2 = 0; j2 < SLAB / 2; ++j2) {
+            const float2 fl2 = mul2(make_float2(ld_as_f32(s_fl, (2 * j2) * kDT), ld_as_f32(s_fl, (2 * j2 + 1) * kDT)), kk);
+            qv[j2] = add2(make_float2(fast_ex2(fl2.x), fast_ex2(fl2.y)), one2);
+          }
+          // Steps past the end of the sequence (last chunk only) arrive as zeros from TMA: they are
+          // made neutral (f = 1), so the chunk's product is the product at the last real step;
+          // u = 0 keeps them out of every sum.
+          const int nvalid = len - SLAB * grp;
+          if (nvalid < SLAB) {
+#pragma unroll
+            for (int j2 = 0; j2 < SLAB / 2; ++j2) {
+              if (2 * j2 >= nvalid) qv[j2].x = 1.f;
+              if (2 * j2 + 1 >= nvalid) qv[j2].y = 1.f;
+            }
+          }
+          float run = 1.f;
+#pragma unroll
+          for (int j2 = 0; j2 < SLAB / 2; ++j2) {
+            L[j2] = mul2(make_float2(run, run), make_float2(qv[j2].x, qv[j2].x * qv[j2].y));
+            run = L[j2].y;
+          }
+        }
+        // (s_L of this stage was last read two tiles back, before those threads' arrivals on `part`,
+        // which completed before the d1_full every thread has waited for in that tile's epilogue)
+        s_L[st][grp][q] = L[SLAB / 2 - 1].y;
+        mbar_arrive_warp(smem_u32(&bars.lprod[st][grp]));
+        // ---- (2) R_t = (products of the groups before) x L_j; operand row chunks of the own slab
+        // (1 / i_t does not depend on the other groups: evaluated before waiting for them)
+        float2 opbv[SLAB / 2];
+#pragma unroll
+        for (int j2 = 0; j2 < SLAB / 2; ++j2) {
+          const float2 il2 = mul2(make_float2(fmaxf(ld_as_f32(s_il, (2 * j2) * kDT), -30.f),
+                                              fmaxf(ld_as_f32(s_il, (2 * j2 + 1) * kDT), -30.f)), kk);
+          opbv[j2] = add2(make_float2(fast_ex2(il2.x), fast_ex2(il2.y)), one2);
+        }
+        float Rstart = 1.f;
+        for (int g2 = 0; g2 < grp; ++g2) {
+          if (!mbar_wait(smem_u32(&bars.lprod[st][g2]), par)) timeout();
+          Rstart *= s_L[st][g2][q];
+        }
+        const float2 Rs2 = make_float2(Rstart, Rstart);
+        unsigned char* a_row = smem + SM::off_AW + st * AW_BYTES + static_cast<uint32_t>(q >> 3) * SBO_AW +
+                               static_cast<uint32_t>(q & 7) * 16;
+        const uint32_t tP = tmem + st * TM_STAGE + lane_off + TM_P + SLAB * grp;
+#pragma unroll
+        for (int j8 = 0; j8 < SLAB / 8; ++j8) {
+          uint32_t hi[4], lo[4], pv[8];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int j2 = 4 * j8 + jj;
+            const float2 opb = opbv[j2];                                                   // 1 / i_t
+            const float2 u2 = make_float2(ld_as_f32(s_u, (2 * j2) * kDT), ld_as_f32(s_u, (2 * j2 + 1) * kDT));
+            const float2 R = mul2(Rs2, L[j2]);
+            const float2 x2 = mul2(R, opb);
+            const float2 r = make_float2(fast_rcp(x2.x), fast_rcp(x2.y));
+            const float2 P = mul2(opb, r);                          // P_t = 1 / R_t
+            pv[2 * jj] = __float_as_uint(P.x);
+            pv[2 * jj + 1] = __float_as_uint(P.y);
+            const float2 w = mul2(u2, mul2(mul2(R, r), R));         // u_t i_t R_t
+            split_pair(w, hi[jj], lo[jj]);
+          }
+          *reinterpret_cast<uint4*>(a_row + (AW_W1 + 2 * grp + j8) * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(a_row + (AW_W2 + 2 * grp + j8) * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(tP + 8 * j8),
+                       "r"(pv[0]), "r"(pv[1]), "r"(pv[2]), "r"(pv[3]), "r"(pv[4]), "r"(pv[5]), "r"(pv[6]), "r"(pv[7]));
+        }
+        mbar_arrive_warp(smem_u32(&bars.empty[slot]));            // the slab has been read
+        // the last group holds the whole chunk's product: the carry warps' P_Q and deep-gate decision
+        // (s_Rend of the tile two back was read before that tile's acc_free, which this thread
+        // waited for in that tile's epilogue)
+        if (grp == NGRP - 1) s_Rend[st][q] = Rstart * L[SLAB / 2 - 1].y;
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        fence_async_smem();
+        mbar_arrive_warp(smem_u32(&bars.part[st][grp]));
+      }
+      // ---- (3) the previous tile's outputs for the same steps
+      if (it > 0) epilogue();
+      if (it < ntotal) {
+        e_b = b; e_d0 = d0; e_t0 = c * Q; e_len = min(Q, p.T - c * Q); e_it = it; e_Dv = Dv;
+        if (++c == nchunks) {
+          c = 0;
+          x += x_step;
+        }
       }
     }
   }
-  if (tid == 0) tma_store_wait_all();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace tc3
-
-#ifdef NAJU_PROF
-}  // namespace naju
-extern "C" int naju_b200_debug_prof3(unsigned long long* out48, int reset) {
-  if (reset) {
-    unsigned long long z[48] = {};
-    return static_cast<int>(cudaMemcpyToSymbol(naju::tc3::g_prof, z, sizeof(z)));
-  }
-  return static_cast<int>(cudaMemcpyFromSymbol(out48, naju::tc3::g_prof, 48 * sizeof(unsigned long long)));
-}
-namespace naju {
-#endif
 
 // ------------------------------------------------------------------------------ host side
 namespace {

@@ -122,6 +122,14 @@ __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
 }
+// One arrival for the whole (converged) warp: 32 lanes arriving on one barrier would be 32
+// serialised updates of the same shared-memory word.  __syncwarp orders the lanes' earlier
+// shared-memory writes before the elected lane's releasing arrival.  Barriers used with this are
+// initialised with a count in WARPS.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t mbar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(mbar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
 }
@@ -130,7 +138,26 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t by
 // the phase completes, so the common case costs one instruction and no wake-up delay; only after
 // 64 failed tries does the loop add a nanosleep, which bounds the whole wait to roughly
 // [2^18 x 0.26 us, 2^18 x 4.3 us] = 0.07 .. 1.1 s.
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
+#define NAJU_STR2(x) #x
+#define NAJU_STR(x) NAJU_STR2(x)
+// One non-blocking look at the barrier: true if the phase of parity `parity` has completed.
+__device__ __forceinline__ bool mbar_try_once(uint32_t mbar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(mbar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// (kept out of line: the retry loop is cold code, and the kernels' hot loops must stay small
+// enough for the instruction caches)
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t mbar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
@@ -141,8 +168,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "@p bra NAJU_MBAR_DONE;\n\t"
       "add.u32 n, n, 1;\n\t"
+#ifdef NAJU_SPIN_SLEEP
+      "nanosleep.u32 " NAJU_STR(NAJU_SPIN_SLEEP) ";\n\t"
+#else
       "setp.gt.u32 q, n, 64;\n\t"
       "@q nanosleep.u32 256;\n\t"
+#endif
       "setp.lt.u32 q, n, %4;\n\t"
       "@q bra NAJU_MBAR_TRY;\n"
       "NAJU_MBAR_DONE:\n\t"
@@ -153,12 +184,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// (the common case -- the phase is already complete -- costs one try and one branch)
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
+  if (mbar_try_once(mbar, parity)) return true;
+  return mbar_wait_slow(mbar, parity);
+}
 
 // The same wait for warps with slack (they are waiting most of the time, and a tight polling loop
 // takes issue slots from the working warps of their scheduler): sleep NS nanoseconds between
 // tries.  Bounded like mbar_wait.
 template <int NS>
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t mbar, uint32_t parity) {
+__device__ __noinline__ bool mbar_wait_relaxed_slow(uint32_t mbar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
@@ -179,6 +215,20 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t mbar, uint32_t parity
       : "r"(mbar), "r"(parity), "r"(4096u), "r"(1u << 22), "n"(NS)
       : "memory");
   return ok != 0;
+}
+template <int NS>
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t mbar, uint32_t parity) {
+  if (mbar_try_once(mbar, parity)) return true;
+  return mbar_wait_relaxed_slow<NS>(mbar, parity);
+}
+
+// For a role that knows its wait is long: look once, sleep FIRST nanoseconds if the phase is not
+// complete yet, then poll every NS nanoseconds (bounded like mbar_wait_relaxed).
+template <int FIRST, int NS>
+__device__ __forceinline__ bool mbar_wait_presleep(uint32_t mbar, uint32_t parity) {
+  if (mbar_try_once(mbar, parity)) return true;
+  if constexpr (FIRST > 0) asm volatile("nanosleep.u32 %0;" ::"n"(FIRST));
+  return mbar_wait_relaxed<NS>(mbar, parity);
 }
 
 // ---- TMA: 3-D tiled load global -> shared, completion counted on an mbarrier.  Plain
