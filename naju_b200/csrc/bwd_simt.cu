@@ -422,7 +422,7 @@ int launch_bwd_simt(const BwdParams& p, const Geometry& g, int act, int gate, vo
   finalize_bc_kernel<<<blocks, 256, 0, st>>>(p.dBpart, dB, rows, g.ndt, g.NS, g.N, p.bc_dtype);
   finalize_bc_kernel<<<blocks, 256, 0, st>>>(p.dCpart, dC, rows, g.ndt, g.NS, g.N, p.bc_dtype);
   finalize_dD_kernel<<<(g.D + 31) / 32, dim3(32, 32), 0, st>>>(p.dDpart, dD, g.nchunks * g.B,
-                                                              p.tc_launched ? 2 * g.B : 0, p.fwd_form,
+                                                              p.tc_launched ? 4 * g.B : 0, p.fwd_form,
                                                               g.ndt * kDT, g.D);
   return static_cast<int>(cudaGetLastError());
 }
