@@ -44,7 +44,7 @@
 //               The same warps turn the cross-channel block's M2 into the masked two-term operand
 //               of the second MMA round.
 //   warp 22     TMA producer (input slabs of 16 steps: u, f_logit, i_logit, dy; raw B / C rows).
-//   warp 23     MMA issuer.
+//   warp 23     MMA issuer (one thread; issuing from two warps was measured and is slower).
 // Every wait is bounded.  Tiles with deep retention gates (prod f < 2^-80 in a chunk) cannot be
 // factorised; the forward records whether it met one, and this kernel stands down in that case
 // (the exact recurrent backward runs instead).
@@ -79,12 +79,20 @@ constexpr uint32_t SBO_M = 16 * 128, M_BYTES = 8 * SBO_M;        // 16384
 constexpr uint32_t BC_BYTES = Q * NS * 2;
 // TMEM columns.  The intra-chunk parts of dC / dB (second MMA round) land in the first 32 columns of
 // the cross-channel block, which has been read out by then.
-constexpr uint32_t TM_Y = 0, TM_G = 64, TM_DL = 128, TM_X = 144, TM_DCI = TM_X, TM_DBI = TM_X + 16, TM_CF = 240,
+// (dL sits directly before gt: one MMA with the B operand [C | g1] accumulates into both)
+constexpr uint32_t TM_Y = 0, TM_DL = 64, TM_G = 80, TM_X = 144, TM_DCI = TM_X, TM_DBI = TM_X + 16, TM_CF = 240,
                    TM_CI = 304, TM_CU = 368, TM_GB = 432, TMEM_COLS = 512;
 constexpr float kRMax = 1.0e24f;
 constexpr float kNegLog2e = -1.4426950408889634f;
 // nanoseconds between polls; waits that are known to be long sleep a first stretch before polling
-constexpr int kRelaxProd = 64, kRelaxBuild = 64, kRelaxCarry = 64, kRelaxMain = 48, kRelaxMma = 32;
+#ifndef RLXB
+#define RLXB 1
+#endif
+#ifndef PRE_MAIN
+#define PRE_MAIN 0
+#define PRE_CARRY 0
+#endif
+constexpr int kRelaxProd = 64 * RLXB, kRelaxBuild = 64 * RLXB, kRelaxCarry = 64 * RLXB, kRelaxMain = 48 * RLXB, kRelaxMma = 32 * RLXB;
 
 __device__ __forceinline__ float fast_ex2(float x) {
   float r;
@@ -374,7 +382,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
     // ===================================================================== MMA issuer
     if (lane == 0) {
       const uint32_t aR = sbase + Smem::off_rows, aM = sbase + Smem::off_M;
-      const uint32_t iKK64 = idesc_bf16(64, 0, 0), iKM64 = idesc_bf16(64, 0, 1), iKM16 = idesc_bf16(16, 0, 1);
+      const uint32_t iKK64 = idesc_bf16(64, 0, 0), iKM64 = idesc_bf16(64, 0, 1), iKM80 = idesc_bf16(80, 0, 1),
+                     iKM16 = idesc_bf16(16, 0, 1);
       const uint32_t iMM96 = idesc_bf16(96, 1, 1), iMM16 = idesc_bf16(16, 1, 1);
       // Every operand address is fixed, so the descriptors are built once; a descriptor for another
       // chunk / row group is the base plus (byte offset >> 4) in its address field.  K-major:
@@ -385,23 +394,32 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       // accumulator row 64+s (the lane of the thread that holds V[s,:]); rows 0-63 are never read
       const uint64_t dMk = umma_desc(aM, 128, SBO_M), dMm = umma_desc(aM - 8 * 128, SBO_M, 128);
       auto off = [](uint32_t bytes) { return static_cast<uint64_t>(bytes >> 4); };
-      for (int it = 0; it < ntotal; ++it) {
-        const uint32_t par = it & 1, st = it % Smem::NBG, par2 = (it / Smem::NBG) & 1;
+      // One tile's MMAs as straight-line code: the operand stage is a compile-time constant and
+      // every slab loop is unrolled.  (Measured: the same MMAs issued from loops with a run-time
+      // trip count or slab index take the kernel 10-15 % longer; an MMA of these shapes occupies
+      // the tensor pipe for about fifty cycles whatever its N, so their number is what counts --
+      // which is why dL rides along with gt in one instruction.)
+      auto tile = [&](auto stc, int it) {
+        constexpr uint32_t st = decltype(stc)::value;
+        const uint32_t par = it & 1, par2 = (it / Smem::NBG) & 1;
         const uint32_t aBG = sbase + Smem::off_BG + st * BG_BYTES, aBB = sbase + Smem::off_BB + st * BB_BYTES;
         const uint64_t dGk = umma_desc(aBG, 128, SBO_BG), dGm = umma_desc(aBG, SBO_BG, 128);  // C | g1 | g2
-        const uint64_t dCm = umma_desc(aBG + BG_C * 128, SBO_BG, 128);                        // C read MN-major (N = state)
+        const uint64_t dCm = umma_desc(aBG + BG_C * 128, SBO_BG, 128);                        // C (| g1) read MN-major
         const uint64_t dBk = umma_desc(aBB, 128, SBO_BB), dBm = umma_desc(aBB, SBO_BB, 128);  // B rows
         if (!mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.ops_full[st]), par2)) timeout();
         // the accumulators and coefficients of the previous tile have been read
         if (it >= 1 && !mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.acc_free), par ^ 1)) timeout();
-        // Yt = (h1 + h2).C   (K = n): the h rows are posted at the very start of a tile
+        // (and its second-round results, which sit in the columns of the cross-channel block: polled
+        // here, long after they were read, rather than between the first round and that block)
+        if (it >= 1 && !mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.x_free), par ^ 1)) timeout();
+        // Yt = (h1 + h2).C   (K = n): the h rows are posted ahead of the tile
         if (!mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.h_full), par)) timeout();
         tc_fence_after();
         umma_bf16(tmem + TM_Y, dRk + off(R_H1 * 128), dGk + off(BG_C * 128), iKK64, 0u);
         umma_bf16(tmem + TM_Y, dRk + off(R_H2 * 128), dGk + off(BG_C * 128), iKK64, 1u);
-#pragma unroll 1
+        // the MMAs that contract over time need only the row chunks of their slab
+#pragma unroll
         for (int ks = 0; ks < NSLAB; ++ks) {
-          // the MMAs that contract over time need only the row chunks of slab ks
           if (!mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.part[ks]), par)) timeout();
           tc_fence_after();
           // Yt += w1.g1 + w1.g2 + w2.g1   (K = s)
@@ -409,14 +427,12 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g1, iKK64, 1u);
           umma_bf16(tmem + TM_Y, dRk + off((R_W1 + 2 * ks) * 128), g2, iKK64, 1u);
           umma_bf16(tmem + TM_Y, dRk + off((R_W2 + 2 * ks) * 128), g1, iKK64, 1u);
-          // gt += al1.g1^T + al1.g2^T + al2.g1^T   (K = t: the G buffer read MN-major)
-          const uint64_t g1t = dGm + off(2 * ks * SBO_BG + BG_G1 * 128), g2t = dGm + off(2 * ks * SBO_BG + BG_G2 * 128);
-          umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g1t, iKM64, ks > 0);
+          // [dL | gt] += al1.[C | g1]^T + al2.[C | g1]^T,  gt += al1.g2^T   (K = t: the [C | g1 | g2]
+          // buffer read MN-major; C and g1 are neighbours, so one MMA feeds both accumulators)
+          const uint64_t cg1 = dCm + off(2 * ks * SBO_BG), g2t = dGm + off(2 * ks * SBO_BG + BG_G2 * 128);
+          umma_bf16(tmem + TM_DL, dRk + off((R_A1 + 2 * ks) * 128), cg1, iKM80, ks > 0);
           umma_bf16(tmem + TM_G, dRk + off((R_A1 + 2 * ks) * 128), g2t, iKM64, 1u);
-          umma_bf16(tmem + TM_G, dRk + off((R_A2 + 2 * ks) * 128), g1t, iKM64, 1u);
-          // dL += al1.C + al2.C   (K = t; the C rows read MN-major)
-          umma_bf16(tmem + TM_DL, dRk + off((R_A1 + 2 * ks) * 128), dCm + off(2 * ks * SBO_BG), iKM16, ks > 0);
-          umma_bf16(tmem + TM_DL, dRk + off((R_A2 + 2 * ks) * 128), dCm + off(2 * ks * SBO_BG), iKM16, 1u);
+          umma_bf16(tmem + TM_DL, dRk + off((R_A2 + 2 * ks) * 128), cg1, iKM80, 1u);
         }
         // gt += (l1 + l2).B   (K = n): the only MMAs that need the whole chunk's retention product
         if (!mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.lt_full), par)) timeout();
@@ -425,11 +441,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         umma_bf16(tmem + TM_G, dRk + off(R_L2 * 128), dBk, iKK64, 1u);
         umma_commit(smem_u32(&bars.d1_full));  // the reverse sweep can start
         // cross-channel: X[m, n'] += [al | wt]^T . [wt | h | lt]   (K = 16 channels per step); these run
-        // on the tensor cores while the main warps do the sweep.  (The previous tile's second-round
-        // results sit in the same columns: they must have been read.)
-        if (it >= 1 && !mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.x_free), par ^ 1)) timeout();
-        tc_fence_after();
-#pragma unroll 1
+        // on the tensor cores while the main warps do the sweep
+#pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t grp = dRm + off(2 * ks * SBO_R);
           umma_bf16(tmem + TM_X, grp + off(R_A1 * 128), grp + off(R_W1 * 128), iMM96, ks > 0);
@@ -437,10 +450,11 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           umma_bf16(tmem + TM_X, grp + off(R_A2 * 128), grp + off(R_W1 * 128), iMM96, 1u);
         }
         umma_commit(smem_u32(&bars.d4_full));
-        // second round: the intra-chunk parts of dC and dB from the masked M2 the carry warps wrote
+        // second round: the intra-chunk parts of dC and dB from the masked M2 the builders wrote
+        // (m2_full also says the cross-channel block has been read out of these columns)
         if (!mbar_wait_relaxed<kRelaxMma>(smem_u32(&bars.m2_full), par)) timeout();
         tc_fence_after();
-#pragma unroll 1
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           // dCi[t,n] += sum_s M2[t,s] B[s,n]    (A = M2 rows, K = s; the B rows read MN-major)
           umma_bf16(tmem + TM_DCI, dMk + off((M_1 + 2 * ks) * 128), dBm + off(2 * ks * SBO_BB), iKM16, ks > 0);
@@ -450,6 +464,14 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           umma_bf16(tmem + TM_DBI, dMm + off(2 * ks * SBO_M + M_2 * 128), dCm + off(2 * ks * SBO_BG), iMM16, 1u);
         }
         umma_commit(smem_u32(&bars.d5_full[st]));
+      };
+      if constexpr (Smem::NBG == 2) {
+        for (int it = 0; it < ntotal; it += 2) {
+          tile(std::integral_constant<uint32_t, 0>{}, it);
+          if (it + 1 < ntotal) tile(std::integral_constant<uint32_t, 1>{}, it + 1);
+        }
+      } else {
+        for (int it = 0; it < ntotal; ++it) tile(std::integral_constant<uint32_t, 0>{}, it);
       }
     }
   } else if (warp >= W_CARRY && warp < W_BUILD) {
@@ -527,7 +549,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
       const int c = nchunks - 1 - ci, t0 = c * Q, len = min(Q, p.T - t0);
       const uint32_t par = it & 1, st = it % Smem::NBG, par2 = (it / Smem::NBG) & 1;
       // ---- the chunk's retention product is known: lt rows
-      if (!mbar_wait_presleep<400, kRelaxCarry>(smem_u32(&bars.rq_ready), par)) timeout();
+      if (!mbar_wait_presleep<PRE_CARRY, kRelaxCarry>(smem_u32(&bars.rq_ready), par)) timeout();
       const float Rend = s_Rend[cid];
       if (!(Rend < kRMax)) atomicOr(&p.hdr->status, NAJU_ST_DEEP_TILE);  // never expected here
       const float PQ = __frcp_rn(Rend);
@@ -724,7 +746,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 
         // ---------------- sweep (1), once the first MMA round is complete: z_t = al_t Yt_t - wt_t gt_t
         // and its suffix sums over the own steps, S_t = sum_{s >= t, own} z_s
-        if (!mbar_wait_presleep<400, kRelaxMain>(smem_u32(&bars.d1_full), par)) timeout();
+        if (!mbar_wait_presleep<PRE_MAIN, kRelaxMain>(smem_u32(&bars.d1_full), par)) timeout();
         tc_fence_after();
         float2 S[SLAB / 2];
         {

@@ -140,7 +140,25 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t by
 // [2^18 x 0.26 us, 2^18 x 4.3 us] = 0.07 .. 1.1 s.
 #define NAJU_STR2(x) #x
 #define NAJU_STR(x) NAJU_STR2(x)
-// One non-blocking look at the barrier: true if the phase of parity `parity` has completed.
+// One look at the barrier without any suspension (test_wait; try_wait may park the thread for a
+// hardware-chosen time when the phase is still open): true if the phase of parity `parity` has
+// completed.
+__device__ __forceinline__ bool mbar_test_once(uint32_t mbar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(mbar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// One try at the barrier (the hardware may park the thread for a short, bounded time before it
+// answers): true if the phase of parity `parity` has completed.
 __device__ __forceinline__ bool mbar_try_once(uint32_t mbar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
