@@ -33,8 +33,8 @@ def resolve_backend(backend=None):
 
 def _form():
     """NAJU_B200_FORM selects the forward kernel family: "auto" (default) takes the tcgen05
-    tensor-core chunked form where it applies (16-bit activations, bf16 B/C, N == 16, TMA-legal
-    strides) and the exact recurrent kernels elsewhere; "recurrent" forces the recurrent ones;
+    tensor-core chunked form where it applies (16-bit activations, bf16 B/C, N == 16 -- or fewer,
+    padded with zero columns by the host when the problem is large enough --, TMA-legal strides) and the exact recurrent kernels elsewhere; "recurrent" forces the recurrent ones;
     "chunked" insists on the tensor-core form and raises where it does not apply."""
     f = os.environ.get("NAJU_B200_FORM", "auto").lower()
     if f not in ("auto", "chunked", "recurrent"):
@@ -130,15 +130,48 @@ def _state_arg(h, B, D, N, name):
     return h.detach().to(torch.float32).contiguous()
 
 
+# ---------------------------------------------------------------------------------------------
+# Fewer than 16 states.  The tcgen05 kernels are built for 16 states; the recurrence
+# (naju/scan.py:87-91) is diagonal in the state index and y only sums over it, so zero columns
+# added to B and C (and to h0 / dhT) change nothing: the host pads N < 16 up to 16 and slices the
+# state-shaped results back.  (The same argument splits N > 16 into groups of 16 states whose
+# y / du / d f_logit / d i_logit are added up; that was built and measured -- 2.2x (N=64) and 3.1x
+# (N=32) faster than the recurrent kernels at B=8, T=8192, D=4096 -- but every group's output is
+# rounded to the 16-bit activation type before the sum, which put y and the gradients at 2.7e-3 of
+# the reference, outside the 1e-3 / 2e-3 bounds, so N > 16 stays with the exact recurrent kernels.)
+_GROUP = 16
+_PAD_MIN_WORK = 1 << 20  # B*T*D below which the recurrent kernels are as fast
+
+
+def _pad_to_group(u, Bm):
+    """True if B and C get zero columns up to 16 states so that the tensor-core form applies."""
+    if Bm.shape[-1] >= _GROUP or _form() == "recurrent":
+        return False
+    if u.dtype not in (torch.bfloat16, torch.float16) or Bm.dtype != torch.bfloat16:
+        return False
+    B, T, D = u.shape
+    return B * T * D >= _PAD_MIN_WORK and T >= 128
+
+
+def _pad_states(t):
+    """Zero columns up to 16 along the last dimension (a copy; these tensors are small)."""
+    if t is None or t.shape[-1] == _GROUP:
+        return t
+    return torch.nn.functional.pad(t, (0, _GROUP - t.shape[-1]))
+
+
 def scan_forward(u, f_logit, i_logit, Bm, Cm, D_skip, h0=None, want_final=False, want_decay=False):
     """Raw forward over prepared tensors.  Returns (y, hT|None, pT|None, ckpt, desc)."""
     lib = _lib.load()
     B, T, D = u.shape
     N = Bm.shape[-1]
+    if _pad_to_group(u, Bm):
+        Bm, Cm, h0 = _pad_states(Bm), _pad_states(Cm), _pad_states(h0)
+    Np = Bm.shape[-1]
     d = _desc(u, f_logit, i_logit, Bm, Cm)
     dev = u.device
     y = torch.empty((B, T, D), dtype=u.dtype, device=dev)
-    hT = torch.empty((B, D, N), dtype=torch.float32, device=dev) if want_final else None
+    hT = torch.empty((B, D, Np), dtype=torch.float32, device=dev) if want_final else None
     pT = torch.empty((B, D), dtype=torch.float32, device=dev) if want_decay else None
     ckpt = _workspace(lib.naju_b200_ckpt_bytes(d), dev)
     scratch = _workspace(lib.naju_b200_fwd_scratch_bytes(d), dev)
@@ -152,22 +185,30 @@ def scan_forward(u, f_logit, i_logit, Bm, Cm, D_skip, h0=None, want_final=False,
             _last_forms["fwd"] = lib.naju_b200_read_form(_ptr(scratch), _stream())
             if st != 0:
                 raise RuntimeError(f"naju_b200_fwd device status {st} (bounded wait ran out)")
+    if want_final and Np != N:
+        hT = hT[..., :N].contiguous()
     return y, hT, pT, ckpt, d
 
 
 def scan_backward(d, u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy, dhT, ckpt, want_dh0=False):
-    """Raw backward.  Returns (du, dfl, dil, dB, dC, dD, dh0|None)."""
+    """Raw backward.  Returns (du, dfl, dil, dB, dC, dD, dh0|None).  `d` and `ckpt` are what
+    scan_forward returned for the same tensors (NAJU_B200_FORM must not change in between: it
+    decides whether fewer than 16 states are padded)."""
     lib = _lib.load()
     B, T, D = u.shape
     N = Bm.shape[-1]
+    if _pad_to_group(u, Bm):
+        Bm, Cm, h0, dhT = _pad_states(Bm), _pad_states(Cm), _pad_states(h0), _pad_states(dhT)
+        d = _desc(u, f_logit, i_logit, Bm, Cm)
+    Np = Bm.shape[-1]
     dev = u.device
     du = torch.empty((B, T, D), dtype=u.dtype, device=dev)
     dfl = torch.empty((B, T, D), dtype=f_logit.dtype, device=dev)
     dil = torch.empty((B, T, D), dtype=f_logit.dtype, device=dev)
-    dB = torch.empty((B, T, N), dtype=Bm.dtype, device=dev)
-    dC = torch.empty((B, T, N), dtype=Bm.dtype, device=dev)
+    dB = torch.empty((B, T, Np), dtype=Bm.dtype, device=dev)
+    dC = torch.empty((B, T, Np), dtype=Bm.dtype, device=dev)
     dD = torch.empty((D,), dtype=torch.float32, device=dev)
-    dh0 = torch.empty((B, D, N), dtype=torch.float32, device=dev) if want_dh0 else None
+    dh0 = torch.empty((B, D, Np), dtype=torch.float32, device=dev) if want_dh0 else None
     scratch = _workspace(lib.naju_b200_bwd_scratch_bytes(d), dev)
     dy = dy.to(u.dtype).contiguous()
     with torch.cuda.device(dev):
@@ -181,6 +222,9 @@ def scan_backward(d, u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy, dhT, ckpt, wan
             _last_forms["bwd"] = lib.naju_b200_read_form(_ptr(scratch), _stream())
             if st != 0:
                 raise RuntimeError(f"naju_b200_bwd device status {st} (bounded wait ran out)")
+    if Np != N:
+        dB, dC = dB[..., :N].contiguous(), dC[..., :N].contiguous()
+        dh0 = None if dh0 is None else dh0[..., :N].contiguous()
     return du, dfl, dil, dB, dC, dD, dh0
 
 
@@ -250,6 +294,11 @@ def _(u, f_logit, i_logit, Bm, Cm, D_skip, h0, want_final):
     B, T, D = u.shape
     N = Bm.shape[-1]
     hT = u.new_empty((B, D, N), dtype=torch.float32) if want_final else u.new_empty(0, dtype=torch.float32)
+    # (fewer than 16 states may be padded to 16: the same rule as scan_forward, on the dtype
+    # the prepared B and C take, see _prepare)
+    bdt = Bm.dtype if (Bm.dtype == Cm.dtype and Bm.dtype in _DT) else torch.float32
+    if _pad_to_group(u, u.new_empty((0, 0, N), dtype=bdt)):
+        N = _GROUP
     ckpt = u.new_empty(_ckpt_bytes_formula(B, T, D, N), dtype=torch.uint8)
     return u.new_empty((B, T, D)), hT, ckpt
 

@@ -84,9 +84,12 @@ def _worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_nccl_hand_off_matches_unsharded_oracle():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_nccl_hand_off_matches_unsharded_oracle(world):
+    """Time-sharded scan over `world` ranks, one process per GPU, NCCL hand-off of (state, decay)
+    (NVLS off, plain send/recv), forward and backward against the unsharded fp64 oracle."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
