@@ -1,8 +1,15 @@
 """Multi-GPU forms of the scan (one process per GPU, torch.distributed for the plumbing).
 
-Batch x channel sharding needs nothing from this module: every (batch row, channel) pair is an
-independent recurrence, so each rank simply calls `naju_scan` on its rows; there is no
+Batch sharding needs nothing from this module but `shard_batch`: every (batch row, channel) pair
+is an independent recurrence, so each rank simply calls `naju_scan` on its rows; there is no
 collective on the data path.
+
+Channel sharding, for batches smaller than the number of GPUs (`naju_scan_channel_sharded`):
+rank r holds the channel slice [r*D/R, (r+1)*D/R) of u, the two logit tensors, D_skip and y,
+and a full copy of B and C.  The forward needs no exchange.  In the backward every gradient
+but two is local to the slice; dB and dC sum over channels, so each rank's are partial sums
+over its own channels and one fp32 all-reduce of the two [B,T,N] tensors completes them
+(2 * B*T*N*4 bytes: 16.8 MB at B=8, T=16384, N=16).
 
 Time sharding, for sequences too long for one GPU: rank r holds the time slice
 [r*T/R, (r+1)*T/R) of every tensor.  The recurrence is affine in the state, so a slice is
@@ -41,7 +48,9 @@ class CudaLocalScan:
     def backward(self, ctx, dy, dhT):
         from . import scan as S
         pu, pf, pi, pB, pC, pD, ph0, ckpt, d = ctx
-        return S.scan_backward(d, pu, pf, pi, pB, pC, pD, ph0, dy, dhT, ckpt, want_dh0=True)
+        # (the terminal adjoint may arrive as a strided view, e.g. a channel slice)
+        pdhT = S._state_arg(dhT, pu.shape[0], pu.shape[2], pB.shape[-1], "dhT")
+        return S.scan_backward(d, pu, pf, pi, pB, pC, pD, ph0, dy, pdhT, ckpt, want_dh0=True)
 
     def dead_prefix_len(self, ctx, T):
         """Number of leading steps after which the carry-in cannot influence y any more
@@ -182,6 +191,62 @@ def naju_scan_time_sharded(u, f_logit, i_logit, B, C, D_skip, group=None, *, h0=
     local = local or CudaLocalScan()
     return _TimeShardedScan.apply(u, f_logit, i_logit, B, C, D_skip, h0, group, local,
                                   bool(return_final_state))
+
+
+class _ChannelShardedScan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, u, fl, il, Bm, Cm, Dk, h0, group, local, want_final, reduce_bc):
+        y, hT, _, lctx = local.forward(u, fl, il, Bm, Cm, Dk, h0)
+        ctx.local, ctx.lctx, ctx.group = local, lctx, group
+        ctx.want_final, ctx.reduce_bc, ctx.has_h0 = want_final, reduce_bc, h0 is not None
+        ctx.in_dtypes = tuple(t.dtype for t in (u, fl, il, Bm, Cm, Dk))
+        if want_final:
+            return y, hT
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dhT=None):
+        term = dhT if (ctx.want_final and dhT is not None) else None
+        du, dfl, dil, dB, dC, dD, dh0 = ctx.local.backward(ctx.lctx, dy.contiguous(), term)
+        if ctx.reduce_bc:
+            # partial sums over this rank's channels -> sums over all channels, in fp32, one
+            # collective for both tensors
+            both = torch.stack([dB.to(torch.float32), dC.to(torch.float32)])
+            dist.all_reduce(both, op=dist.ReduceOp.SUM, group=ctx.group)
+            dB, dC = both[0], both[1]
+        t = ctx.in_dtypes
+        return (du.to(t[0]), dfl.to(t[1]), dil.to(t[2]), dB.to(t[3]), dC.to(t[4]), dD.to(t[5]),
+                dh0 if ctx.has_h0 else None, None, None, None, None)
+
+
+def naju_scan_channel_sharded(u, f_logit, i_logit, B, C, D_skip, group=None, *, h0=None,
+                              return_final_state=False, reduce_bc=True, local=None):
+    """Scan whose CHANNEL axis is split across the ranks of `group` (for batches smaller than
+    the group).
+
+    Every rank passes its channel slice of u, f_logit, i_logit ([B, T, D_r]), D_skip ([D_r]) and
+    h0 ([B, D_r, N]), and the full B and C ([B, T, N], the same on every rank); it gets its slice
+    of y (and of the final state).  The forward exchanges nothing.  Gradients of the sliced
+    tensors are local.  dB and dC sum over channels: with reduce_bc=True (default) they are
+    completed by one fp32 all-reduce over the group, so every rank returns the full gradient of
+    its copy of B and C; with reduce_bc=False each rank returns its partial sums and the caller
+    adds them (e.g. together with other gradients of a replicated tensor).
+    """
+    if reduce_bc and not dist.is_initialized():
+        raise RuntimeError("naju_scan_channel_sharded(reduce_bc=True) needs an initialised torch.distributed group")
+    local = local or CudaLocalScan()
+    return _ChannelShardedScan.apply(u, f_logit, i_logit, B, C, D_skip, h0, group, local,
+                                     bool(return_final_state), bool(reduce_bc))
+
+
+def shard_channels(t, rank, world, dim=-1, multiple=128):
+    """Channels of `t` along `dim` owned by `rank`: contiguous slices whose length is a multiple of
+    `multiple` (the kernels tile channels by 128) except possibly the last."""
+    D = t.shape[dim]
+    per = (D + world - 1) // world
+    per = (per + multiple - 1) // multiple * multiple
+    lo, hi = min(D, rank * per), min(D, (rank + 1) * per)
+    return t.narrow(dim, lo, hi - lo)
 
 
 def shard_batch(t, rank, world):

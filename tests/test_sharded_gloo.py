@@ -107,6 +107,62 @@ def test_time_sharded_matches_unsharded_oracle(world):
     assert oracle.rel_l2(res[0]["dh0"], g["dh0"]) < 2e-6
 
 
+def _worker_channels(rank, world, port, q, reduce_bc):
+    import oracle
+    from naju_b200.sharded import naju_scan_channel_sharded, shard_channels
+    _init(rank, world, port)
+    B, T, D, N = 2, 40, 20, 16
+    d = oracle.make_inputs(B, T, D, N, seed=6, f_shift=2.0, d_skip_scale=0.01, with_h0=True)
+    sl = lambda a, dim: shard_channels(torch.tensor(a), rank, world, dim=dim, multiple=4).clone()
+    t = {k: sl(d[k], 2).requires_grad_(True) for k in ("u", "fl", "il")}
+    t["Bm"], t["Cm"] = (torch.tensor(d[k]).requires_grad_(True) for k in ("Bm", "Cm"))
+    Dk = sl(d["Dskip"], 0).requires_grad_(True)
+    h0 = sl(d["h0"], 1).requires_grad_(True)
+    y, hT = naju_scan_channel_sharded(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], Dk, None, h0=h0,
+                                      return_final_state=True, reduce_bc=reduce_bc, local=OracleLocalScan())
+    torch.autograd.backward([y, hT], [sl(d["dy"], 2), sl(d["dhT"], 1)])
+    q.put(dict(rank=rank, y=y.detach().numpy(), hT=hT.detach().numpy(), dD=Dk.grad.numpy(),
+               dh0=h0.grad.numpy(), **{"d" + k: t[k].grad.numpy() for k in t}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,reduce_bc", [(2, True), (3, True), (2, False)])
+def test_channel_sharded_matches_unsharded_oracle(world, reduce_bc):
+    """Channel slices per rank, B and C replicated: y, the states and the sliced gradients are
+    local; dB / dC are partial sums over the rank's channels, completed by one all-reduce
+    (reduce_bc=True: every rank holds the full sums) or left to the caller (False: they add up)."""
+    import oracle
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_channels, args=(r, world, port, q, reduce_bc)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=120) for _ in range(world)], key=lambda r: r["rank"])
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    B, T, D, N = 2, 40, 20, 16
+    d = oracle.make_inputs(B, T, D, N, seed=6, f_shift=2.0, d_skip_scale=0.01, with_h0=True)
+    a = (d["u"], d["fl"], d["il"], d["Bm"], d["Cm"], d["Dskip"])
+    y, hT = oracle.oracle_fwd(*a, h0=d["h0"], return_final_state=True)
+    g = oracle.oracle_bwd(*a, d["dy"], h0=d["h0"], dhT=d["dhT"])
+    cat = lambda k, ax: np.concatenate([r[k] for r in res], axis=ax)
+    assert oracle.rel_l2(cat("y", 2), y) < 1e-6
+    assert oracle.rel_l2(cat("hT", 1), hT) < 1e-6
+    for k, gk in (("du", "du"), ("dfl", "dfl"), ("dil", "dil")):
+        assert oracle.rel_l2(cat(k, 2), g[gk]) < 2e-6, k
+    assert oracle.rel_l2(cat("dD", 0), g["dD"]) < 2e-6
+    assert oracle.rel_l2(cat("dh0", 1), g["dh0"]) < 2e-6
+    for k, gk in (("dBm", "dB"), ("dCm", "dC")):
+        if reduce_bc:
+            for r in res:
+                assert oracle.rel_l2(r[k], g[gk]) < 2e-6, k
+        else:
+            assert oracle.rel_l2(sum(r[k] for r in res), g[gk]) < 2e-6, k
+
+
 def _worker_fault(rank, world, port, q, mode):
     from naju_b200.sharded import chain_forward
     try:
@@ -155,6 +211,17 @@ def test_hand_off_failures_surface_as_errors_not_hangs(mode):
     assert got[1].startswith("error"), got     # the receiving rank raised instead of hanging
     if mode == "wrong_shape":
         assert "mismatch" in got[1]
+
+
+def test_shard_channels_partitions_in_tile_multiples():
+    from naju_b200.sharded import shard_channels
+    t = torch.arange(2 * 3 * 1000).view(2, 3, 1000)
+    parts = [shard_channels(t, r, 3) for r in range(3)]
+    assert torch.equal(torch.cat(parts, dim=-1), t)
+    assert [p.shape[-1] for p in parts] == [384, 384, 232]
+    parts = [shard_channels(t, r, 8, dim=2, multiple=128) for r in range(8)]
+    assert torch.equal(torch.cat(parts, dim=2), t)
+    assert [p.shape[2] for p in parts] == [128] * 7 + [104]
 
 
 def test_shard_batch_partitions_rows():
