@@ -72,20 +72,8 @@ constexpr uint32_t BC_BYTES = Q * NS * 2;
 constexpr uint32_t TM_D1 = 0, TM_D2 = 64, TM_P = 96, TM_G = 160, TM_STAGE = 224, TMEM_COLS = 512;
 constexpr float kRMax = 1.0e24f;  // ~2^80
 constexpr float kNegLog2e = -1.4426950408889634f;
-// nanoseconds between polls for the roles that have slack; the main warps and the MMA issuer poll
-// without sleeping
-#ifndef RLX_P
-#define RLX_P 1000
-#define RLX_B 400
-#define RLX_C 200
-#define RLX_S 500
-#endif
-constexpr int kRelaxProd = RLX_P, kRelaxBuild = RLX_B, kRelaxCarry = RLX_C, kRelaxStore = RLX_S;
-#ifndef PRE_B
-#define PRE_B 0
-#define PRE_C 0
-#define PRE_S 0
-#endif
+// Every wait parks the warp in mbarrier.try_wait (the hardware wakes it when the phase completes);
+// sleeping between polls instead, for the roles with slack, was measured and is 1 % slower.
 
 __device__ __forceinline__ float fast_ex2(float x) {
   float r;
@@ -267,7 +255,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
         for (int c = 0; c < nchunks; ++c, ++it) {
           const int t0 = c * Q;
-          if (it >= 2 && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.bc_empty[it & 1]), ((it >> 1) & 1) ^ 1)) timeout();
+          if (it >= 2 && !mbar_wait(smem_u32(&bars.bc_empty[it & 1]), ((it >> 1) & 1) ^ 1)) timeout();
           {
             const uint32_t bar = smem_u32(&bars.bc_full[it & 1]);
             const uint32_t dst = sbase + SM::off_bc + (it & 1) * 2 * BC_BYTES;
@@ -277,7 +265,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           }
           for (int k = 0; k < NSLAB; ++k, ++slab) {
             const uint32_t slot = slab % SM::RING, ph = (slab / SM::RING) & 1;
-            if (slab >= SM::RING && !mbar_wait_relaxed<kRelaxProd>(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
+            if (slab >= SM::RING && !mbar_wait(smem_u32(&bars.empty[slot]), ph ^ 1)) timeout();
             const uint32_t bar = smem_u32(&bars.full[slot]);
             const uint32_t dst = sbase + SM::off_ring + slot * SM::slab_bytes;
             mbar_arrive_expect_tx(bar, SM::slab_bytes);
@@ -297,9 +285,9 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
     for (int it = 0; it < ntotal; ++it) {
       const int st = it & 1;
       const uint32_t par = (it >> 1) & 1;
-      if (!mbar_wait_relaxed<kRelaxBuild>(smem_u32(&bars.bc_full[st]), par)) timeout();
+      if (!mbar_wait(smem_u32(&bars.bc_full[st]), par)) timeout();
       // stage st: the MMAs of the tile two back must have read B1 / BB (its epilogue may still run)
-      if (it >= NSTAGE && !mbar_wait_presleep<PRE_B, kRelaxBuild>(smem_u32(&bars.d1_full[st]), par ^ 1)) timeout();
+      if (it >= NSTAGE && !mbar_wait(smem_u32(&bars.d1_full[st]), par ^ 1)) timeout();
       unsigned char* s_B1 = smem + SM::off_B1 + st * B1_BYTES;
       unsigned char* s_BB = smem + SM::off_BB + st * BB_BYTES;
       const __nv_bfloat16* Braw = reinterpret_cast<const __nv_bfloat16*>(smem + SM::off_bc + st * 2 * BC_BYTES);
@@ -410,7 +398,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         const int b = x / p.ndt, d0 = (x - b * p.ndt) * kDT;
         for (int c = 0; c < nchunks; ++c, ++it) {
           const int st = it & 1;
-          if (!mbar_wait_presleep<PRE_S, kRelaxStore>(smem_u32(&bars.y_staged[st]), (it >> 1) & 1)) timeout();
+          if (!mbar_wait(smem_u32(&bars.y_staged[st]), (it >> 1) & 1)) timeout();
           if (!s_store_deep[st]) {
             // the staged tile leaves by TMA (steps past T and channels past D are clipped); the stage
             // is released once the store has read it
@@ -468,7 +456,7 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
       tcd.d_ok = tcd.d < p.D;
       for (int c = 0; c < nchunks; ++c, ++it) {
         const int st = it & 1;
-        if (!mbar_wait_presleep<PRE_C, kRelaxCarry>(smem_u32(&bars.d2_full[st]), (it >> 1) & 1)) timeout();
+        if (!mbar_wait(smem_u32(&bars.d2_full[st]), (it >> 1) & 1)) timeout();
         if (!mbar_wait(smem_u32(&bars.part[st][NGRP - 1]), (it >> 1) & 1)) timeout();  // (the writers of s_Rend arrived here)
         tcd.c = c;
         tcd.tile = static_cast<int64_t>(c) * ctiles + x;
