@@ -43,11 +43,13 @@ CFG = dict(B=8, T=16384, D=2048, N=16)
 FALLBACK_HBM_GBS = 6650.0
 
 
-def algorithmic_bytes(B, T, D, N, e=2):
+def algorithmic_bytes(B, T, D, N, e=2, eg=None):
     """Per-launch algorithmic HBM bytes: forward reads u,fl,il,B,C and writes y;
-    backward reads u,fl,il,dy,B,C and writes du,dfl,dil,dB,dC."""
+    backward reads u,fl,il,dy,B,C and writes du,dfl,dil,dB,dC.  e = element size of the
+    activations, eg = of the logits and their gradients (e unless given)."""
     tok = B * T
-    return tok * (4 * D * e + 2 * N * e), tok * (7 * D * e + 4 * N * e)
+    eg = e if eg is None else eg
+    return tok * (2 * D * e + 2 * D * eg + 2 * N * e), tok * (3 * D * e + 4 * D * eg + 4 * N * e)
 
 
 def measured_peak():
@@ -237,8 +239,13 @@ def run_gpu_arm(args):
         return torch.randn(*s, device=dev, generator=g)
 
     u = rn(B, T, D).to(dt)
-    fl = (rn(B, T, D) + 2.0).to(dt)
-    il = rn(B, T, D).to(dt)
+    if args.layout == "mixer":
+        # as the mixer hands the tensors over under bf16 autocast (naju/mixer.py:106-118): u is the
+        # depthwise convolution's [B,D,T] output viewed as [B,T,D]; the logits are fp32
+        u = u.transpose(1, 2).contiguous().transpose(1, 2)
+    gdt = torch.float32 if args.layout == "mixer" else dt
+    fl = (rn(B, T, D) + 2.0).to(gdt)
+    il = rn(B, T, D).to(gdt)
     Bm = (rn(B, T, N) / N ** 0.5).to(dt)
     Cm = (rn(B, T, N) / N ** 0.5).to(dt)
     Dk = torch.zeros(D, device=dev)
@@ -346,7 +353,7 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
         tokens = B * T * world
         ms_per_step = total_ms / args.steps
         value = tokens / (ms_per_step / 1e3)
-        fwd_bytes, bwd_bytes = algorithmic_bytes(B, T, D, N)
+        fwd_bytes, bwd_bytes = algorithmic_bytes(B, T, D, N, eg=4 if args.layout == "mixer" else 2)
         peak, peak_kind = measured_peak()
         achieved = bwd_bytes / (bwd_ms / 1e3) / 1e9
         is_metric = (B, T, D, N) == (CFG["B"], CFG["T"], CFG["D"], CFG["N"])
@@ -357,7 +364,9 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
             "data": "synthetic",
             "config": {"workload": ("metric: " if is_metric else "other: ") +
                        f"scan fwd+bwd B={B} T={T} D={D} N={N} per GPU",
-                       "io_dtype": "bf16", "state_dtype": "f32", "sharding": f"batch x{world}, no collective",
+                       "io_dtype": "bf16" if args.layout == "reference" else
+                       "bf16 u/B/C, fp32 logits; u time-contiguous ([B,D,T] memory), as naju/mixer.py hands them over",
+                       "state_dtype": "f32", "sharding": f"batch x{world}, no collective",
                        "l2": "inputs larger than L2 (no flush needed)",
                        "d_skip": "zeros, as the mixer passes them (the skip is applied outside the scan)",
                        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
@@ -466,6 +475,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--shape", default=None, help="B,T,D,N instead of the metric workload (profiling)")
+    ap.add_argument("--layout", default="reference", choices=["reference", "mixer"],
+                    help="reference = contiguous bf16 [B,T,D] tensors (the metric); mixer = u in [B,D,T] memory "
+                         "and fp32 logits, as the mixer produces them (a side measurement, not the metric)")
     ap.add_argument("--workload", default="train", choices=["train", "decode"],
                     help="train = the headline fwd+bwd scan; decode = the single-token state update")
     args = ap.parse_args()

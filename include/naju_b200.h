@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define NAJU_B200_ABI_VERSION 1
+#define NAJU_B200_ABI_VERSION 2
 
 /* element types of caller tensors */
 enum { NAJU_F32 = 0, NAJU_BF16 = 1, NAJU_F16 = 2 };
@@ -82,7 +82,13 @@ enum {
  * Strides are in ELEMENTS.  The innermost (channel / state) stride of every
  * tensor is 1.  u/f_logit/i_logit may each have their own batch and time
  * strides (the mixer hands Bm and Cm as two views of one [B,T,2N] tensor,
- * naju/mixer.py:116, so their time stride is 2N there). */
+ * naju/mixer.py:116, so their time stride is 2N there).
+ * One exception: u may be TIME-contiguous -- the [B,D,T] memory the mixer's depthwise
+ * convolution leaves behind, viewed as [B,T,D] (naju/mixer.py:115).  Then u_st = 1 and
+ * u_sd > 1 is the element stride between channels; element (b,t,d) of u sits at
+ * b*u_sb + t + d*u_sd.  u_sd = 0 or 1 means the usual channel-contiguous u.  The backward then
+ * writes du with u's strides (the gradient of a [B,D,T] tensor is wanted in [B,D,T] memory);
+ * every other tensor keeps its channel-contiguous layout. */
 typedef struct naju_scan_desc {
   int32_t B, T, D, N;
   int32_t act_dtype;  /* u, y, dy, du            */
@@ -94,6 +100,7 @@ typedef struct naju_scan_desc {
   int64_t il_sb, il_st;
   int64_t bm_sb, bm_st;
   int64_t cm_sb, cm_st;
+  int64_t u_sd;       /* 0 / 1: u is channel-contiguous; > 1: time-contiguous u, see above */
 } naju_scan_desc;
 
 /* ABI version of the loaded library (NAJU_B200_ABI_VERSION it was built with). */

@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnaju_b200.so")
 
 NAJU_F32, NAJU_BF16, NAJU_F16 = 0, 1, 2
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 ST_LOOKBACK_TIMEOUT = 1
 ST_BAD_TILE = 2
@@ -42,7 +42,8 @@ class ScanDesc(ctypes.Structure):
                 ("fl_sb", ctypes.c_int64), ("fl_st", ctypes.c_int64),
                 ("il_sb", ctypes.c_int64), ("il_st", ctypes.c_int64),
                 ("bm_sb", ctypes.c_int64), ("bm_st", ctypes.c_int64),
-                ("cm_sb", ctypes.c_int64), ("cm_st", ctypes.c_int64)]
+                ("cm_sb", ctypes.c_int64), ("cm_st", ctypes.c_int64),
+                ("u_sd", ctypes.c_int64)]
 
 
 _lib = None

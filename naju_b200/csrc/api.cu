@@ -27,7 +27,12 @@ int check_desc(const naju_scan_desc* d, bool need_T) {
 }
 
 int check_strides(const naju_scan_desc* d) {
-  if (d->u_st < d->D || d->fl_st < d->D || d->il_st < d->D) return NAJU_E_STRIDE;
+  if (d->u_sd > 1) {  // time-contiguous u: channels u_sd apart, steps adjacent
+    if (d->u_st != 1 || d->u_sd < d->T) return NAJU_E_STRIDE;
+  } else if (d->u_sd < 0 || d->u_st < d->D) {
+    return NAJU_E_STRIDE;
+  }
+  if (d->fl_st < d->D || d->il_st < d->D) return NAJU_E_STRIDE;
   if (d->bm_st < d->N || d->cm_st < d->N) return NAJU_E_STRIDE;
   if (d->u_sb < 0 || d->fl_sb < 0 || d->il_sb < 0 || d->bm_sb < 0 || d->cm_sb < 0) return NAJU_E_STRIDE;
   return NAJU_OK;
@@ -40,6 +45,7 @@ void fill_common(P& p, const naju_scan_desc* d, const Geometry& g) {
   p.u_sb = d->u_sb; p.u_st = d->u_st; p.fl_sb = d->fl_sb; p.fl_st = d->fl_st;
   p.il_sb = d->il_sb; p.il_st = d->il_st; p.bm_sb = d->bm_sb; p.bm_st = d->bm_st;
   p.cm_sb = d->cm_sb; p.cm_st = d->cm_st;
+  p.u_sd = d->u_sd > 1 ? d->u_sd : 1;
 }
 
 __global__ void copy_state_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n,
@@ -203,7 +209,10 @@ int naju_b200_fwd(const naju_scan_desc* desc, const void* u, const void* f_logit
   int rck = -1000;
   if (!(desc->flags & NAJU_FLAG_RECURRENT_ONLY)) {
     rck = launch_fwd_tc3(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
-    if (rck == -1000) rck = launch_fwd_tc2(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
+    // (the ticket kernel reads u channel-contiguous only; a time-contiguous u that the walk kernel
+    // declines goes to the recurrent kernel, which transposes its tile while staging it)
+    if (rck == -1000 && p.u_sd == 1)
+      rck = launch_fwd_tc2(p, g, desc->act_dtype, desc->gate_dtype, desc->bc_dtype, stream);
     if (rck == -1000 && (desc->flags & NAJU_FLAG_CHUNKED_ONLY)) return NAJU_E_UNSUPPORTED;
   }
   if (rck == -1000) rck = launch_fwd_simt(p, g, desc->act_dtype, desc->gate_dtype, stream);

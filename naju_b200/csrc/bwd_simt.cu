@@ -67,8 +67,11 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
   const int d = d0 + tid;
   const bool d_ok = d < p.D;
 
-  load_tile_async(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 * p.u_st + d0, p.u_st,
-                  len, cols, tid);
+  if (p.u_sd > 1)
+    load_tile_tmajor(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 + d0 * p.u_sd, p.u_sd, len, cols, tid);
+  else
+    load_tile_async(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 * p.u_st + d0, p.u_st,
+                    len, cols, tid);
   load_tile_async(s_dy, reinterpret_cast<const TA*>(p.dy) + (static_cast<int64_t>(b) * p.T + t0) * p.D + d0,
                   static_cast<int64_t>(p.D), len, cols, tid);
   load_tile_async(s_fl, reinterpret_cast<const TG*>(p.fl) + b * p.fl_sb + t0 * p.fl_st + d0,
@@ -333,7 +336,10 @@ __global__ void __launch_bounds__(kThreads) bwd_simt_kernel(const BwdParams p) {
   }
 
   const int64_t out_off = (static_cast<int64_t>(b) * p.T + t0) * p.D + d0;
-  store_tile(reinterpret_cast<TA*>(p.du) + out_off, s_u, static_cast<int64_t>(p.D), len, cols, tid);
+  if (p.u_sd > 1)   // du in the layout of a time-contiguous u
+    store_tile_tmajor(reinterpret_cast<TA*>(p.du) + b * p.u_sb + t0 + d0 * p.u_sd, s_u, p.u_sd, len, cols, tid);
+  else
+    store_tile(reinterpret_cast<TA*>(p.du) + out_off, s_u, static_cast<int64_t>(p.D), len, cols, tid);
   store_tile(reinterpret_cast<TG*>(p.dfl) + out_off, s_fl, static_cast<int64_t>(p.D), len, cols, tid);
   store_tile(reinterpret_cast<TG*>(p.dil) + out_off, s_il, static_cast<int64_t>(p.D), len, cols, tid);
   }

@@ -174,7 +174,7 @@ struct Bars {
   unsigned long long acc_free;         // main + carry warps: Yt, gt, dL, coefficients read
 };
 
-template <typename TA, typename TG>
+template <typename TA, typename TG, bool UTM>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* __restrict__ fwd_form) {
   using Smem = SmemT<TG>;
@@ -240,6 +240,9 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
   tc_fence_after();
   const uint32_t tmem = s_tmem;
   auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
+  // u is time-contiguous: its slabs sit in shared memory as [channel][step], du goes out in the same
+  // layout.  (A compile-time switch: as a run-time one it cost the usual layout registers and 18 %.)
+  constexpr bool utm = UTM;
 
   if (warp == W_PROD) {
     // ===================================================================== TMA producer
@@ -264,7 +267,9 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
             const uint32_t bar = smem_u32(&bars.full[slot]);
             const uint32_t dst = sbase + Smem::off_ring + slot * Smem::slab_bytes;
             mbar_arrive_expect_tx(bar, Smem::slab_bytes);
-            tma_load_3d(dst, &maps.u, d0, t0 + k * SLAB, b, bar);
+            // (a time-contiguous u is mapped (T, D, B): its slab lands as [channel][step])
+            if (utm) tma_load_3d(dst, &maps.u, t0 + k * SLAB, d0, b, bar);
+            else tma_load_3d(dst, &maps.u, d0, t0 + k * SLAB, b, bar);
             tma_load_3d(dst + Smem::off_sfl, &maps.fl, d0, t0 + k * SLAB, b, bar);
             tma_load_3d(dst + Smem::off_sil, &maps.il, d0, t0 + k * SLAB, b, bar);
             tma_load_3d(dst + Smem::off_sdy, &maps.dy, d0, t0 + k * SLAB, b, bar);
@@ -647,7 +652,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         const uint32_t sidx = static_cast<uint32_t>(it) * NSLAB + grp, slot = sidx % Smem::RING, ph = (sidx / Smem::RING) & 1;
         if (!mbar_wait(smem_u32(&bars.full[slot]), ph)) timeout();
         const unsigned char* sl = smem + Smem::off_ring + slot * Smem::slab_bytes;
-        const TA* s_u = reinterpret_cast<const TA*>(sl) + cid;
+        const TA* s_u = reinterpret_cast<const TA*>(sl) + cid;          // [step][channel]
+        const TA* s_ut = reinterpret_cast<const TA*>(sl) + cid * SLAB;   // [channel][step] (time-contiguous u)
         const TG* s_fl = reinterpret_cast<const TG*>(sl + Smem::off_sfl) + cid;
         const TG* s_il = reinterpret_cast<const TG*>(sl + Smem::off_sil) + cid;
         const TA* s_dy = reinterpret_cast<const TA*>(sl + Smem::off_sdy) + cid;
@@ -697,7 +703,8 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
                                                 fmaxf(ld_as_f32(s_il, (2 * j2 + 1) * kDT), -30.f)), kk);
             const float2 bq = make_float2(fast_ex2(il2.x), fast_ex2(il2.y));
             const float2 opb = add2(bq, one2);                      // 1 / i_t
-            const float2 u2 = make_float2(ld_as_f32(s_u, (2 * j2) * kDT), ld_as_f32(s_u, (2 * j2 + 1) * kDT));
+            const float2 u2 = utm ? ld_pair_as_f32(s_ut + 2 * j2)
+                                  : make_float2(ld_as_f32(s_u, (2 * j2) * kDT), ld_as_f32(s_u, (2 * j2 + 1) * kDT));
             const float2 dy2 = make_float2(ld_as_f32(s_dy, (2 * j2) * kDT), ld_as_f32(s_dy, (2 * j2 + 1) * kDT));
             const float2 R = mul2(Rs2, L[j2]);
             const float2 Rprev = make_float2(j2 == 0 ? Rstart : Rstart * L[j2 == 0 ? 0 : j2 - 1].y, R.x);
@@ -772,7 +779,11 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
         }
         const float2 rs2 = make_float2(rstart, rstart), Dv2 = make_float2(Dv, Dv);
         const int64_t row0 = (static_cast<int64_t>(b) * p.T + t0 + SLAB * grp) * p.D + d;
-        TA* gdu = reinterpret_cast<TA*>(p.du) + row0;
+        // (du of a time-contiguous u goes out in u's layout: this thread's 16 steps are 32 adjacent
+        // bytes of its channel's row)
+        TA* gdu = utm ? reinterpret_cast<TA*>(p.du) + static_cast<int64_t>(b) * p.u_sb + static_cast<int64_t>(d) * p.u_sd +
+                            t0 + SLAB * grp
+                      : reinterpret_cast<TA*>(p.du) + row0;
         TG* gdfl = reinterpret_cast<TG*>(p.dfl) + row0;
         TG* gdil = reinterpret_cast<TG*>(p.dil) + row0;
         const TA* gdy = reinterpret_cast<const TA*>(p.dy) + row0;
@@ -785,6 +796,7 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
           tmem_ld8_async(trow + TM_CI + 8 * j8, i8);
           tmem_ld8_async(trow + TM_CU + 8 * j8, u8);
           tmem_ld_wait8(i8, u8);
+          [[maybe_unused]] uint32_t dupk[4];
 #pragma unroll
           for (int jj = 3; jj >= 0; --jj) {
             const int j2 = 4 * j8 + jj, j = 2 * j2;
@@ -798,15 +810,28 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
               const float y1 = ok1 ? to_f32(gdy[static_cast<int64_t>(j + 1) * p.D]) : 0.f;
               du = fma2(Dv2, make_float2(y0, y1), du);
             }
+            if constexpr (utm) dupk[jj] = pack_bf16x2(du.x, du.y);
             if (ok0) {
-              gdu[static_cast<int64_t>(j) * p.D] = from_f32<TA>(du.x);
+              if constexpr (!utm) gdu[static_cast<int64_t>(j) * p.D] = from_f32<TA>(du.x);
               gdfl[static_cast<int64_t>(j) * p.D] = from_f32<TG>(dfl.x);
               gdil[static_cast<int64_t>(j) * p.D] = from_f32<TG>(dil.x);
             }
             if (ok1) {
-              gdu[static_cast<int64_t>(j + 1) * p.D] = from_f32<TA>(du.y);
+              if constexpr (!utm) gdu[static_cast<int64_t>(j + 1) * p.D] = from_f32<TA>(du.y);
               gdfl[static_cast<int64_t>(j + 1) * p.D] = from_f32<TG>(dfl.y);
               gdil[static_cast<int64_t>(j + 1) * p.D] = from_f32<TG>(dil.y);
+            }
+          }
+          if constexpr (utm) if (d_ok) {
+            // eight steps of this channel's du: one 16-byte store when all of them are real
+            if (8 * j8 + 8 <= nvalid) {
+              *reinterpret_cast<uint4*>(gdu + 8 * j8) = make_uint4(dupk[0], dupk[1], dupk[2], dupk[3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (8 * j8 + e < nvalid)
+                  reinterpret_cast<unsigned short*>(gdu)[8 * j8 + e] =
+                      static_cast<unsigned short>(e & 1 ? dupk[e >> 1] >> 16 : dupk[e >> 1] & 0xFFFFu);
             }
           }
         }
@@ -827,10 +852,10 @@ bwd_tc_kernel(const BwdParams p, const __grid_constant__ Maps maps, const int* _
 // Launches the tensor-core backward for this problem if it can take it; returns -1000 if not.
 // The kernel itself stands down unless *fwd_form says the forward ran chunked without deep tiles.
 namespace {
-template <typename TA, typename TG>
+template <typename TA, typename TG, bool UTM>
 int launch_bwd_tc_t(const BwdParams& p, const tcb::Maps& maps, const int* fwd_form, int64_t ctiles, cudaStream_t st) {
   constexpr size_t smem = tcb::SmemT<TG>::total;
-  auto kern = tcb::bwd_tc_kernel<TA, TG>;
+  auto kern = tcb::bwd_tc_kernel<TA, TG, UTM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   const int64_t grid = std::min<int64_t>(ctiles, tmah::sm_count());
@@ -850,16 +875,20 @@ int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int 
   if (!(ctiles * 3 >= tmah::sm_count() && g.nchunks >= 4)) return -1000;
   tcb::Maps maps = {};
   const bool ok =
-      tmah::make_map(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB) &&
+      (p.u_sd > 1 ? tmah::make_map_tmajor(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_sd, tcb::SLAB, kDT)
+                  : tmah::make_map(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tcb::SLAB)) &&
       tmah::make_map(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tcb::SLAB) &&
       tmah::make_map(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tcb::SLAB) &&
       tmah::make_map(&maps.dy, p.dy, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tcb::SLAB) &&
       tmah::make_map(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tcb::NS, tcb::Q) &&
       tmah::make_map(&maps.cm, p.Cm, bc, g.B, g.T, g.N, p.cm_sb, p.cm_st, tcb::NS, tcb::Q);
   if (!ok) return -1000;
-  if (gate == NAJU_F32)
-    return launch_bwd_tc_t<__nv_bfloat16, float>(p, maps, fwd_form, ctiles, static_cast<cudaStream_t>(stream));
-  return launch_bwd_tc_t<__nv_bfloat16, __nv_bfloat16>(p, maps, fwd_form, ctiles, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p.u_sd > 1)
+    return gate == NAJU_F32 ? launch_bwd_tc_t<__nv_bfloat16, float, true>(p, maps, fwd_form, ctiles, st)
+                            : launch_bwd_tc_t<__nv_bfloat16, __nv_bfloat16, true>(p, maps, fwd_form, ctiles, st);
+  return gate == NAJU_F32 ? launch_bwd_tc_t<__nv_bfloat16, float, false>(p, maps, fwd_form, ctiles, st)
+                          : launch_bwd_tc_t<__nv_bfloat16, __nv_bfloat16, false>(p, maps, fwd_form, ctiles, st);
 }
 
 }  // namespace naju

@@ -114,6 +114,30 @@ __device__ __forceinline__ void load_tile_async(T* __restrict__ dst, const T* __
   }
 }
 
+// The same tile from a TIME-contiguous source: element (row r, channel c) sits at
+// src[c * chan_stride + r].  Thread c walks its channel's steps; plain stores, visible after the
+// block barrier that follows the staging.  (The slow, general path for this layout: the walk-along-
+// time tensor-core kernels take it natively.)
+template <typename T>
+__device__ __forceinline__ void load_tile_tmajor(T* __restrict__ dst, const T* __restrict__ src,
+                                                 int64_t chan_stride, int rows, int cols_valid, int tid) {
+  if (tid < kDT) {
+    const T* s = src + static_cast<int64_t>(tid) * chan_stride;
+    for (int r = 0; r < rows; ++r) dst[r * kDT + tid] = tid < cols_valid ? s[r] : from_f32<T>(0.f);
+  }
+}
+
+// ... and the store to a TIME-contiguous destination: element (row r, channel c) goes to
+// dst[c * chan_stride + r].
+template <typename T>
+__device__ __forceinline__ void store_tile_tmajor(T* __restrict__ dst, const T* __restrict__ src,
+                                                  int64_t chan_stride, int rows, int cols_valid, int tid) {
+  if (tid < cols_valid) {
+    T* d = dst + static_cast<int64_t>(tid) * chan_stride;
+    for (int r = 0; r < rows; ++r) d[r] = src[r * kDT + tid];
+  }
+}
+
 // Writes a dense [rows][kDT] shared tile to a row-major global tensor window.
 template <typename T>
 __device__ __forceinline__ void store_tile(T* __restrict__ dst, const T* __restrict__ src,

@@ -42,8 +42,11 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const FwdParams p) {
   const int b = tc.b, t0 = tc.t0, len = tc.len, d0 = tc.d0, cols = tc.cols;
 
   // ---- stage the tile
-  load_tile_async(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 * p.u_st + d0, p.u_st,
-                  len, cols, tid);
+  if (p.u_sd > 1)
+    load_tile_tmajor(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 + d0 * p.u_sd, p.u_sd, len, cols, tid);
+  else
+    load_tile_async(s_u, reinterpret_cast<const TA*>(p.u) + b * p.u_sb + t0 * p.u_st + d0, p.u_st,
+                    len, cols, tid);
   load_tile_async(s_fl, reinterpret_cast<const TG*>(p.fl) + b * p.fl_sb + t0 * p.fl_st + d0,
                   p.fl_st, len, cols, tid);
   load_tile_async(s_il, reinterpret_cast<const TG*>(p.il) + b * p.il_sb + t0 * p.il_st + d0,

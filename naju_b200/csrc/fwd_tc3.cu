@@ -149,7 +149,7 @@ __device__ __forceinline__ void split_pair(float2 v, uint32_t& hi, uint32_t& lo)
 template <typename TA, typename TG>
 __device__ __noinline__ void exact_tile_from_global(const FwdParams& p, const TileCoord& tc, int tid,
                                                     float (&hw)[NS], float& Pw) {
-  const TA* gu = reinterpret_cast<const TA*>(p.u) + tc.b * p.u_sb + static_cast<int64_t>(tc.t0) * p.u_st + tc.d;
+  const TA* gu = reinterpret_cast<const TA*>(p.u) + tc.b * p.u_sb + static_cast<int64_t>(tc.t0) * p.u_st + tc.d * p.u_sd;
   const TG* gf = reinterpret_cast<const TG*>(p.fl) + tc.b * p.fl_sb + static_cast<int64_t>(tc.t0) * p.fl_st + tc.d;
   const TG* gi = reinterpret_cast<const TG*>(p.il) + tc.b * p.il_sb + static_cast<int64_t>(tc.t0) * p.il_st + tc.d;
   const int64_t bbase = tc.b * p.bm_sb + static_cast<int64_t>(tc.t0) * p.bm_st;
@@ -187,7 +187,7 @@ __device__ __noinline__ void exact_tile_from_global(const FwdParams& p, const Ti
 // Channel tiles (one batch row x 128 channels) are dealt round-robin over the grid; a CTA walks
 // each of its channel tiles along time, chunk by chunk.  `it` counts the (channel tile, chunk)
 // pairs a CTA has seen and selects the pipeline stage and barrier phases.
-template <typename TA, typename TG>
+template <typename TA, typename TG, bool UTM>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
   using SM = Smem<TG>;
@@ -245,6 +245,9 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
   tc_fence_after();
   const uint32_t tmem = s_tmem;
   auto timeout = [&]() { atomicOr(&p.hdr->status, NAJU_ST_MMA_TIMEOUT); };
+  // u is time-contiguous: its slabs sit in shared memory as [channel][step].  (A compile-time
+  // switch: as a run-time one it cost the usual layout 5 %.)
+  constexpr bool utm = UTM;
 
   if (warp == W_PROD) {
     // ===================================================================== TMA producer
@@ -269,7 +272,9 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
             const uint32_t bar = smem_u32(&bars.full[slot]);
             const uint32_t dst = sbase + SM::off_ring + slot * SM::slab_bytes;
             mbar_arrive_expect_tx(bar, SM::slab_bytes);
-            tma_load_3d(dst, &maps.u, d0, t0 + k * SLAB, b, bar);
+            // (a time-contiguous u is mapped (T, D, B): its slab lands as [channel][step])
+            if (utm) tma_load_3d(dst, &maps.u, t0 + k * SLAB, d0, b, bar);
+            else tma_load_3d(dst, &maps.u, d0, t0 + k * SLAB, b, bar);
             tma_load_3d(dst + SLAB * kDT * 2, &maps.fl, d0, t0 + k * SLAB, b, bar);
             tma_load_3d(dst + SLAB * kDT * (2 + sizeof(TG)), &maps.il, d0, t0 + k * SLAB, b, bar);
           }
@@ -530,7 +535,8 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         tmem_ld16_async(tb + TM_D1, v);
         tmem_ld16_async(tb + TM_P, pv);
         unsigned char* dst = smem + SM::off_Y + ys * (Q * kDT * 2) + (SLAB * grp) * (kDT * 2) + q * 2;
-        const TA* gu = reinterpret_cast<const TA*>(p.u) + e_b * p.u_sb + static_cast<int64_t>(e_t0 + SLAB * grp) * p.u_st + e_d0 + q;
+        const TA* gu = reinterpret_cast<const TA*>(p.u) + e_b * p.u_sb + static_cast<int64_t>(e_t0 + SLAB * grp) * p.u_st +
+                       static_cast<int64_t>(e_d0 + q) * p.u_sd;
         tmem_ld_wait16(v);
         tmem_ld_wait16(pv);
 #pragma unroll
@@ -582,7 +588,8 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
         // ---- (1) retention of the own 16 steps: L_j = prod_{i<=j} (1 + e^{-f_logit_i}), as pairs
         if (!mbar_wait(smem_u32(&bars.full[slot]), ph)) timeout();
         const unsigned char* sl = smem + SM::off_ring + slot * SM::slab_bytes;
-        const TA* s_u = reinterpret_cast<const TA*>(sl) + q;
+        const TA* s_u = reinterpret_cast<const TA*>(sl) + q;          // [step][channel]
+        const TA* s_ut = reinterpret_cast<const TA*>(sl) + q * SLAB;   // [channel][step] (time-contiguous u)
         const TG* s_fl = reinterpret_cast<const TG*>(sl + SLAB * kDT * 2) + q;
         const TG* s_il = s_fl + SLAB * kDT;
         float2 L[SLAB / 2];
@@ -640,7 +647,8 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
           for (int jj = 0; jj < 4; ++jj) {
             const int j2 = 4 * j8 + jj;
             const float2 opb = opbv[j2];                                                   // 1 / i_t
-            const float2 u2 = make_float2(ld_as_f32(s_u, (2 * j2) * kDT), ld_as_f32(s_u, (2 * j2 + 1) * kDT));
+            const float2 u2 = utm ? ld_pair_as_f32(s_ut + 2 * j2)
+                                  : make_float2(ld_as_f32(s_u, (2 * j2) * kDT), ld_as_f32(s_u, (2 * j2 + 1) * kDT));
             const float2 R = mul2(Rs2, L[j2]);
             const float2 x2 = mul2(R, opb);
             const float2 r = make_float2(fast_rcp(x2.x), fast_rcp(x2.y));
@@ -684,10 +692,10 @@ fwd_tc3_kernel(const FwdParams p, const __grid_constant__ Maps maps) {
 // ------------------------------------------------------------------------------ host side
 namespace {
 
-template <typename TA, typename TG>
+template <typename TA, typename TG, bool UTM>
 int launch_tc3_t(const FwdParams& p, const Geometry& g, const tc3::Maps& maps, cudaStream_t st) {
   const size_t smem = tc3::Smem<TG>::total;
-  auto kern = tc3::fwd_tc3_kernel<TA, TG>;
+  auto kern = tc3::fwd_tc3_kernel<TA, TG, UTM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   // one persistent CTA per SM; channel tiles are dealt round-robin
@@ -710,7 +718,8 @@ int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act, int gate, int
   if (static_cast<int64_t>(g.B) * g.ndt * 3 < tmah::sm_count() || g.nchunks < 4) return -1000;
   tc3::Maps maps;
   const bool ok =
-      tmah::make_map(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tc3::SLAB) &&
+      (p.u_sd > 1 ? tmah::make_map_tmajor(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_sd, tc3::SLAB, kDT)
+                  : tmah::make_map(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_st, kDT, tc3::SLAB)) &&
       tmah::make_map(&maps.fl, p.fl, gate, g.B, g.T, g.D, p.fl_sb, p.fl_st, kDT, tc3::SLAB) &&
       tmah::make_map(&maps.il, p.il, gate, g.B, g.T, g.D, p.il_sb, p.il_st, kDT, tc3::SLAB) &&
       tmah::make_map(&maps.bm, p.Bm, bc, g.B, g.T, g.N, p.bm_sb, p.bm_st, tc3::NS, tc3::Q) &&
@@ -718,10 +727,16 @@ int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act, int gate, int
       tmah::make_map(&maps.y, p.y, act, g.B, g.T, g.D, static_cast<int64_t>(g.T) * g.D, g.D, kDT, tc3::Q);
   if (!ok) return -1000;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (act == NAJU_BF16 && gate == NAJU_BF16) return launch_tc3_t<__nv_bfloat16, __nv_bfloat16>(p, g, maps, st);
-  if (act == NAJU_BF16 && gate == NAJU_F32) return launch_tc3_t<__nv_bfloat16, float>(p, g, maps, st);
-  if (act == NAJU_F16 && gate == NAJU_F16) return launch_tc3_t<__half, __half>(p, g, maps, st);
-  if (act == NAJU_F16 && gate == NAJU_F32) return launch_tc3_t<__half, float>(p, g, maps, st);
+  if (p.u_sd > 1) {
+    if (act == NAJU_BF16 && gate == NAJU_BF16) return launch_tc3_t<__nv_bfloat16, __nv_bfloat16, true>(p, g, maps, st);
+    if (act == NAJU_BF16 && gate == NAJU_F32) return launch_tc3_t<__nv_bfloat16, float, true>(p, g, maps, st);
+    if (act == NAJU_F16 && gate == NAJU_F16) return launch_tc3_t<__half, __half, true>(p, g, maps, st);
+    if (act == NAJU_F16 && gate == NAJU_F32) return launch_tc3_t<__half, float, true>(p, g, maps, st);
+  }
+  if (act == NAJU_BF16 && gate == NAJU_BF16) return launch_tc3_t<__nv_bfloat16, __nv_bfloat16, false>(p, g, maps, st);
+  if (act == NAJU_BF16 && gate == NAJU_F32) return launch_tc3_t<__nv_bfloat16, float, false>(p, g, maps, st);
+  if (act == NAJU_F16 && gate == NAJU_F16) return launch_tc3_t<__half, __half, false>(p, g, maps, st);
+  if (act == NAJU_F16 && gate == NAJU_F32) return launch_tc3_t<__half, float, false>(p, g, maps, st);
   return -1000;
 }
 

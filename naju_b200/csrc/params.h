@@ -116,6 +116,7 @@ struct FwdParams {
   float* aggS;
   int B, T, D, N, nchunks, ndt, bc_dtype;
   int64_t u_sb, u_st, fl_sb, fl_st, il_sb, il_st, bm_sb, bm_st, cm_sb, cm_st;
+  int64_t u_sd;  // element stride between channels of u: 1, or > 1 for a time-contiguous u (then u_st == 1)
 };
 
 struct BwdParams {
@@ -138,6 +139,7 @@ struct BwdParams {
   float* dDpart;
   int B, T, D, N, nchunks, ndt, bc_dtype;
   int64_t u_sb, u_st, fl_sb, fl_st, il_sb, il_st, bm_sb, bm_st, cm_sb, cm_st;
+  int64_t u_sd;  // element stride between channels of u: 1, or > 1 for a time-contiguous u (then u_st == 1)
 };
 
 // launchers implemented in the .cu files; return a CUDA runtime error code (0 = ok)

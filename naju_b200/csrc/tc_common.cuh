@@ -328,6 +328,14 @@ __device__ __forceinline__ float ld_as_f32(const __nv_bfloat16* p, int i) {
 }
 __device__ __forceinline__ float ld_as_f32(const __half* p, int i) { return __half2float(p[i]); }
 __device__ __forceinline__ float ld_as_f32(const float* p, int i) { return p[i]; }
+// two adjacent 16-bit elements (4-byte aligned) as floats, one 32-bit load
+__device__ __forceinline__ float2 ld_pair_as_f32(const __nv_bfloat16* p) {
+  const uint32_t pk = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(bf16lo_f32(pk), bf16hi_f32(pk));
+}
+__device__ __forceinline__ float2 ld_pair_as_f32(const __half* p) {
+  return __half22float2(*reinterpret_cast<const __half2*>(p));
+}
 
 // D(16x8, fp32) += A(16x16, bf16, row) . B(16x8, bf16, col)
 __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,

@@ -55,6 +55,25 @@ inline bool make_map(CUtensorMap* m, const void* base, int dt, int64_t B, int64_
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Map of a [B][T][D] tensor stored TIME-contiguous, element strides (sb, 1, sd): TMA dimensions
+// (T, D, B), box = (box_t, box_d, 1); a tile lands in shared memory as [box_d][box_t].
+inline bool make_map_tmajor(CUtensorMap* m, const void* base, int dt, int64_t B, int64_t T, int64_t D, int64_t sb,
+                            int64_t sd, int box_t, int box_d) {
+  const int es = dt == NAJU_F32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+  if ((sd * es) % 16 != 0 || (sb * es) % 16 != 0 || (box_t * es) % 16 != 0) return false;
+  if (sd < T || (B > 1 && sb < sd)) return false;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(sd * es), static_cast<cuuint64_t>((B > 1 ? sb : sd * D) * es)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_t), static_cast<cuuint32_t>(box_d), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  return fn(m, tm_dtype(dt), 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // SM count of the CURRENT device (cached per device ordinal; a racing first call at worst asks twice).
 inline int sm_count() {
   constexpr int kMaxDev = 64;

@@ -64,6 +64,18 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+def _time_contig(u):
+    """True for a [B,T,D] view of [B,D,T] memory (time stride 1, channels T or more apart) that
+    the kernels can take as it is: what the mixer's depthwise convolution leaves behind
+    (naju/mixer.py:115).  TMA wants the channel and batch strides to be multiples of 16 bytes."""
+    if u.dim() != 3 or u.shape[1] < 2 or u.shape[2] < 2:
+        return False
+    sb, st, sd = u.stride()
+    es = u.element_size()
+    return (st == 1 and sd >= u.shape[1] and sb >= 0 and u.data_ptr() % 16 == 0 and
+            (sd * es) % 16 == 0 and (sb * es) % 16 == 0 and (u.shape[0] == 1 or sb >= sd * u.shape[2]))
+
+
 def _inner_contig(t):
     """Tensors whose last stride is 1 and whose outer strides are non-negative pass through."""
     if t.stride(-1) == 1 and all(s >= 0 for s in t.stride()) and t.data_ptr() % t.element_size() == 0:
@@ -91,7 +103,9 @@ def _prepare(u, f_logit, i_logit, Bm, Cm, D_skip):
     i_logit = i_logit.to(gdt)
     bdt = Bm.dtype if (Bm.dtype == Cm.dtype and Bm.dtype in _DT) else torch.float32
     Bm, Cm = Bm.to(bdt), Cm.to(bdt)
-    u, f_logit, i_logit, Bm, Cm = map(_inner_contig, (u, f_logit, i_logit, Bm, Cm))
+    if not _time_contig(u):   # (a time-contiguous u goes to the kernels without a copy)
+        u = _inner_contig(u)
+    f_logit, i_logit, Bm, Cm = map(_inner_contig, (f_logit, i_logit, Bm, Cm))
     D_skip = D_skip.detach().to(torch.float32).contiguous()
     return u, f_logit, i_logit, Bm, Cm, D_skip
 
@@ -107,6 +121,7 @@ def _desc(u, f_logit, i_logit, Bm, Cm):
     if os.environ.get("NAJU_B200_INJECT_TIMEOUT", "0") == "1":  # fault injection for tests
         d.flags |= _lib.FLAG_INJECT_TIMEOUT
     d.u_sb, d.u_st = u.stride(0), u.stride(1)
+    d.u_sd = u.stride(2) if (u.stride(2) != 1 and u.stride(1) == 1) else 1
     d.fl_sb, d.fl_st = f_logit.stride(0), f_logit.stride(1)
     d.il_sb, d.il_st = i_logit.stride(0), i_logit.stride(1)
     d.bm_sb, d.bm_st = Bm.stride(0), Bm.stride(1)
@@ -202,7 +217,9 @@ def scan_backward(d, u, f_logit, i_logit, Bm, Cm, D_skip, h0, dy, dhT, ckpt, wan
         d = _desc(u, f_logit, i_logit, Bm, Cm)
     Np = Bm.shape[-1]
     dev = u.device
-    du = torch.empty((B, T, D), dtype=u.dtype, device=dev)
+    # (a time-contiguous u gets its gradient in the same layout: naju_b200.h, naju_scan_desc)
+    du = torch.empty_strided((B, T, D), u.stride(), dtype=u.dtype, device=dev) if d.u_sd > 1 else \
+        torch.empty((B, T, D), dtype=u.dtype, device=dev)
     dfl = torch.empty((B, T, D), dtype=f_logit.dtype, device=dev)
     dil = torch.empty((B, T, D), dtype=f_logit.dtype, device=dev)
     dB = torch.empty((B, T, Np), dtype=Bm.dtype, device=dev)

@@ -27,7 +27,8 @@ def test_exports_every_declared_symbol(lib):
 
 
 def test_version_and_strerror(lib):
-    assert lib.naju_b200_version() == 1
+    from naju_b200 import _lib
+    assert lib.naju_b200_version() == _lib.ABI_VERSION == 2
     assert lib.naju_b200_strerror(0) == b"ok"
     assert b"NULL" in lib.naju_b200_strerror(-1)
 

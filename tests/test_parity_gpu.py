@@ -428,3 +428,53 @@ def test_fewer_than_16_states_take_the_tensor_core_form(case):
         assert oracle.rel_l2(t[src].grad.float().cpu().numpy(), ref) < TOL_GRAD, k
     if state:
         assert oracle.rel_l2(t["h0"].grad.cpu().numpy(), g["dh0"]) < TOL_GRAD
+
+
+@pytest.mark.parametrize("case", [
+    # tensor-core walk kernels, forward and backward, D_skip and states
+    (4, 520, 2432, 16, 2.0, torch.bfloat16, torch.bfloat16, WALK, WALK),
+    # ... with fp32 logits (the mixer's dtypes) and a partial channel tile
+    (4, 520, 2440, 16, 2.0, torch.bfloat16, torch.float32, WALK, WALK),
+    # deep gates: exact tiles in the forward, recurrent backward (transposing tile loader)
+    (4, 264, 2432, 16, -2.5, torch.bfloat16, torch.bfloat16, WALK, RECURRENT),
+    # too few channel tiles for the walk: the ticket kernel does not take this layout, the
+    # recurrent kernels do
+    (2, 1000, 384, 16, 2.0, torch.bfloat16, torch.bfloat16, RECURRENT, RECURRENT),
+    # fp32 everything (recurrent kernels)
+    (2, 200, 300, 16, 2.0, torch.float32, torch.float32, RECURRENT, RECURRENT)])
+def test_time_contiguous_u_is_taken_without_a_copy(case):
+    """u as the mixer's depthwise convolution leaves it: [B,D,T] memory viewed as [B,T,D]
+    (naju/mixer.py:115).  The host hands it to the kernels as it is (same data pointer, channel
+    stride in the descriptor); the walk kernels read it through a (T, D, B) tensor map, the
+    recurrent kernels transpose their tile while staging it.  Forward, final state and all
+    gradients against the fp64 oracle on the same quantised inputs; kernel forms asserted."""
+    from naju_b200 import naju_scan
+    from naju_b200 import scan as S
+    B, T, D, N, fs, dt, gdt, ffwd, fbwd = case
+    d = oracle.make_inputs(B, T, D, N, seed=17, f_shift=fs, d_skip_scale=0.05, with_h0=True)
+    cast = {"u": dt, "Bm": dt, "Cm": dt, "dy": dt, "fl": gdt, "il": gdt}
+    q = {k: (_round(d[k], cast[k]) if k in cast else d[k]) for k in d}
+    t = {k: torch.tensor(q[k], device="cuda").to(cast.get(k, torch.float32)) for k in ("u", "fl", "il", "Bm", "Cm", "Dskip", "h0")}
+    t["u"] = t["u"].transpose(1, 2).contiguous().transpose(1, 2)      # [B,D,T] memory
+    assert t["u"].stride() == (D * T, 1, T)
+    for k in t:
+        t[k].requires_grad_(True)
+    pu = S._prepare(t["u"].detach(), t["fl"].detach(), t["il"].detach(), t["Bm"].detach(), t["Cm"].detach(),
+                    t["Dskip"].detach())[0]
+    assert pu.data_ptr() == t["u"].data_ptr() and pu.stride() == t["u"].stride()      # no copy
+    y, hT = naju_scan(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], t["Dskip"], h0=t["h0"], return_final_state=True)
+    torch.autograd.backward([y, hT], [torch.tensor(q["dy"], device="cuda").to(dt), torch.tensor(d["dhT"], device="cuda")])
+    torch.cuda.synchronize()
+    assert _forms() == {"fwd": ffwd, "bwd": fbwd}
+    a = (q["u"], q["fl"], q["il"], q["Bm"], q["Cm"], q["Dskip"])
+    yo, hTo = oracle.oracle_fwd(*a, h0=q["h0"], return_final_state=True)
+    g = oracle.oracle_bwd(*a, q["dy"], h0=q["h0"], dhT=d["dhT"])
+    f32 = dt == torch.float32
+    tol_f, tol_g = (TIGHT_FWD, TIGHT_GRAD) if f32 else (TOL_FWD, TOL_GRAD)
+    assert oracle.rel_l2(hT.detach().cpu().numpy(), hTo) < tol_f
+    assert oracle.rel_l2(y.detach().float().cpu().numpy(), _round(yo, dt)) < tol_f
+    for k, src in GRADS:
+        gd = torch.float32 if k == "dD" else gdt if k in ("dfl", "dil") else dt
+        assert t[src].grad.shape == t[src].shape
+        assert oracle.rel_l2(t[src].grad.float().cpu().numpy(), _round(g[k], gd)) < tol_g, k
+    assert oracle.rel_l2(t["h0"].grad.cpu().numpy(), g["dh0"]) < tol_g
