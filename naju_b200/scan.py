@@ -132,9 +132,41 @@ def _desc(u, f_logit, i_logit, Bm, Cm):
     return d
 
 
+_GUARD = 4096          # bytes of canary on each side of a workspace when NAJU_B200_GUARD=1
+_GUARD_BYTE = 0xA5
+_guarded = []          # (whole buffer, payload size) of the workspaces handed out since the last check
+
+
 def _workspace(nbytes, device):
-    # torch's caching allocator returns 512-byte aligned blocks
-    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    """Caller-owned workspace for the library (torch's caching allocator returns 512-byte aligned
+    blocks).  With NAJU_B200_GUARD=1 every workspace sits between two canary bands that
+    check_workspace_guards() verifies: the stand-in for a memory checker on the kernels' writes to
+    checkpoint and scratch buffers (a debug aid; off by default)."""
+    n = max(int(nbytes), 256)
+    if os.environ.get("NAJU_B200_GUARD", "0") != "1":
+        return torch.empty(n, dtype=torch.uint8, device=device)
+    n_al = (n + 255) // 256 * 256
+    whole = torch.empty(_GUARD + n_al + _GUARD, dtype=torch.uint8, device=device)
+    whole[:_GUARD] = _GUARD_BYTE
+    whole[_GUARD + n:] = _GUARD_BYTE
+    _guarded.append((whole, n))
+    return whole[_GUARD:_GUARD + n]
+
+
+def check_workspace_guards():
+    """Verifies (and forgets) the canary bands of every workspace handed out under
+    NAJU_B200_GUARD=1 since the last call; raises if a kernel wrote outside its workspace.
+    Synchronises the device."""
+    bad = []
+    for whole, n in _guarded:
+        lo, hi = whole[:_GUARD], whole[_GUARD + n:]
+        if bool((lo != _GUARD_BYTE).any()) or bool((hi != _GUARD_BYTE).any()):
+            bad.append((int(whole.numel()), n))
+    count = len(_guarded)
+    _guarded.clear()
+    if bad:
+        raise RuntimeError(f"workspace guard bands overwritten: {bad}")
+    return count
 
 
 def _state_arg(h, B, D, N, name):

@@ -17,8 +17,10 @@ summarised by (S_r, P_r) = (its final state from a zero start, the product of it
 gates), and only those two small tensors cross NVLink:
 
   1. every rank scans its slice from a zero state (rank 0: from h0), in parallel;
-  2. the carry h_in,r+1 = P_r * h_in,r + S_r runs down the chain with send/recv
-     ([B,D,N] + [B,D] fp32 per hop; received tensors land in this rank's own memory);
+  2. every rank learns every slice's (S_r, P_r) with ONE all_gather ([B,D,N] + [B,D] fp32 per
+     rank, received into this rank's own memory) and folds the slices before its own,
+     h_in,r+1 = P_r * h_in,r + S_r, locally -- no serial chain of hops, no host round trip
+     (`handoff="chain"` keeps the older send/recv chain with a shape header per hop);
   3. ranks whose carry-in is non-zero scan again from the true h_in -- under no_grad only the
      leading part of the slice, up to the chunk where the cumulative retention product has
      decayed below 1e-30 in every channel and the carry can no longer change y.
@@ -113,6 +115,40 @@ def chain_forward(S, P, h0, group):
     return h_in, h_out
 
 
+def gather_forward(S, P, h0, group):
+    """Step 2 with one collective: all ranks' (S, P) are gathered and the carry entering this
+    rank's slice is the fold of the slices before it.  Returns (h_in, h_out) like chain_forward."""
+    rank, world = _group_info(group)
+    pack = torch.cat([S.reshape(S.shape[0], -1), P.reshape(P.shape[0], -1)], dim=1).contiguous()
+    got = [torch.empty_like(pack) for _ in range(world)]
+    dist.all_gather(got, pack, group=group)
+    nS = S[0].numel()
+    h = torch.zeros_like(S) if h0 is None else h0.to(S.dtype)   # (S of rank 0 already contains h0)
+    h_in = h
+    for k in range(rank):
+        Sk = got[k][:, :nS].reshape(S.shape)
+        Pk = got[k][:, nS:].reshape(P.shape)
+        h_in = Sk if k == 0 else Pk.unsqueeze(-1) * h_in + Sk
+    if rank == 0:
+        return h, S
+    return h_in, P.unsqueeze(-1) * h_in + S
+
+
+def gather_backward(L, P, group):
+    """Adjoint hand-off with one collective; returns (lam_in, lam_out) like chain_backward."""
+    rank, world = _group_info(group)
+    pack = torch.cat([L.reshape(L.shape[0], -1), P.reshape(P.shape[0], -1)], dim=1).contiguous()
+    got = [torch.empty_like(pack) for _ in range(world)]
+    dist.all_gather(got, pack, group=group)
+    nL = L[0].numel()
+    lam_in = torch.zeros_like(L)
+    for k in range(world - 1, rank, -1):
+        Lk = got[k][:, :nL].reshape(L.shape)
+        Pk = got[k][:, nL:].reshape(P.shape)
+        lam_in = Pk.unsqueeze(-1) * lam_in + Lk
+    return lam_in, P.unsqueeze(-1) * lam_in + L
+
+
 def chain_backward(L, P, group):
     """Adjoint chain.  L [B,D,N] = this slice's dh0 for a zero adjoint from later slices.
     Returns (lam_in, lam_out): the adjoint entering this slice from the future (zero on the
@@ -130,14 +166,14 @@ def chain_backward(L, P, group):
 
 class _TimeShardedScan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, u, fl, il, Bm, Cm, Dk, h0, group, local, want_final):
+    def forward(ctx, u, fl, il, Bm, Cm, Dk, h0, group, local, want_final, handoff):
         rank, world = _group_info(group)
         T = u.shape[1]
         needs_grad = any(ctx.needs_input_grad[:7])
         first_h0 = h0 if rank == 0 else None
         y, S, P, lctx = local.forward(u, fl, il, Bm, Cm, Dk, first_h0)
-        h_in, h_out = chain_forward(S, P, first_h0, group)
-        if rank > 0 and bool((h_in != 0).any().item()):
+        h_in, h_out = (gather_forward if handoff == "all_gather" else chain_forward)(S, P, first_h0, group)
+        if rank > 0:   # (no look at the carry's values: that would be a host round trip)
             if needs_grad:
                 y, _, _, lctx = local.forward(u, fl, il, Bm, Cm, Dk, h_in)
             else:
@@ -147,7 +183,7 @@ class _TimeShardedScan(torch.autograd.Function):
                 y = y.clone() if not y.is_contiguous() else y
                 y[:, :n] = y_fix
         ctx.local, ctx.lctx, ctx.group, ctx.P = local, lctx, group, P
-        ctx.want_final = want_final
+        ctx.want_final, ctx.handoff = want_final, handoff
         ctx.has_h0 = h0 is not None
         ctx.in_dtypes = tuple(t.dtype for t in (u, fl, il, Bm, Cm, Dk))
         ctx.mark_non_differentiable(P)
@@ -163,20 +199,20 @@ class _TimeShardedScan(torch.autograd.Function):
         term = dh_out if (ctx.want_final and dh_out is not None) else None
         # pass A: zero adjoint from the future (plus this rank's own terminal adjoint)
         gA = local.backward(ctx.lctx, dy, term)
-        lam_in, lam_out = chain_backward(gA[6], P, group)
+        lam_in, lam_out = (gather_backward if ctx.handoff == "all_gather" else chain_backward)(gA[6], P, group)
         g = gA
-        if rank < world - 1 and bool((lam_in != 0).any().item()):
+        if rank < world - 1:
             total = lam_in if term is None else lam_in + term.to(lam_in.dtype)
             g = local.backward(ctx.lctx, dy, total)
             lam_out = g[6]
         t = ctx.in_dtypes
         dh0 = lam_out if (ctx.has_h0 and rank == 0) else None
         return (g[0].to(t[0]), g[1].to(t[1]), g[2].to(t[2]), g[3].to(t[3]), g[4].to(t[4]),
-                g[5].to(t[5]), dh0, None, None, None)
+                g[5].to(t[5]), dh0, None, None, None, None)
 
 
 def naju_scan_time_sharded(u, f_logit, i_logit, B, C, D_skip, group=None, *, h0=None,
-                           return_final_state=False, local=None):
+                           return_final_state=False, local=None, handoff="all_gather"):
     """Scan of a sequence whose time axis is split across the ranks of `group`.
 
     Every rank passes ITS slice ([B, T_r, D] / [B, T_r, N]) and gets its slice of y.  `h0`
@@ -184,13 +220,17 @@ def naju_scan_time_sharded(u, f_logit, i_logit, B, C, D_skip, group=None, *, h0=
     (state at the end of this rank's slice, product of the retention gates over the slice);
     the global final state is the one on the last rank.  Gradients: each rank receives the
     gradients of its own slices; D_skip's gradient is this rank's partial sum (sum over ranks
-    for the total, like any replicated parameter); dh0 arrives on rank 0.
+    for the total, like any replicated parameter); dh0 arrives on rank 0.  `handoff` selects how
+    the slice summaries travel: "all_gather" (one collective, default) or "chain" (send/recv
+    from rank to rank with a shape header per hop).
     """
     if not dist.is_initialized():
         raise RuntimeError("naju_scan_time_sharded needs an initialised torch.distributed group")
+    if handoff not in ("all_gather", "chain"):
+        raise ValueError("handoff must be 'all_gather' or 'chain'")
     local = local or CudaLocalScan()
     return _TimeShardedScan.apply(u, f_logit, i_logit, B, C, D_skip, h0, group, local,
-                                  bool(return_final_state))
+                                  bool(return_final_state), handoff)
 
 
 class _ChannelShardedScan(torch.autograd.Function):

@@ -117,3 +117,27 @@ def test_torch_compile_fullgraph_matches_eager(monkeypatch, shape, dtype, state)
     assert abs(float(out) - ref_val) <= 1e-5 * abs(ref_val)
     for x, r in zip(leaves, ref):
         assert oracle.rel_l2(x.grad.float().cpu().numpy(), r.float().cpu().numpy()) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(4, 520, 2440, 16, torch.bfloat16), (2, 1000, 200, 16, torch.bfloat16),
+                                   (2, 300, 130, 24, torch.float32), (1, 65, 64, 100, torch.float32)])
+def test_kernels_stay_inside_their_workspaces(monkeypatch, shape):
+    """NAJU_B200_GUARD=1 puts canary bands around the checkpoint and scratch buffers of every call;
+    after a forward and a backward in each kernel family (walk, ticket, recurrent; partial channel
+    tiles, ragged T, wide states) the bands must be intact."""
+    from naju_b200 import naju_scan
+    from naju_b200 import scan as S
+    monkeypatch.setenv("NAJU_B200_GUARD", "1")
+    S.check_workspace_guards()
+    B, T, D, N, dt = shape
+    g = torch.Generator(device="cuda").manual_seed(3)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    u, fl, il = r(B, T, D).to(dt).requires_grad_(), (r(B, T, D) + 2).to(dt).requires_grad_(), r(B, T, D).to(dt).requires_grad_()
+    Bm, Cm = (r(B, T, N) / N ** 0.5).to(dt).requires_grad_(), (r(B, T, N) / N ** 0.5).to(dt).requires_grad_()
+    Dk = torch.zeros(D, device="cuda").requires_grad_()
+    h0 = r(B, D, N).requires_grad_()
+    y, hT = naju_scan(u, fl, il, Bm, Cm, Dk, h0=h0, return_final_state=True)
+    torch.autograd.backward([y, hT], [r(B, T, D).to(dt), r(B, D, N)])
+    torch.cuda.synchronize()
+    assert S.check_workspace_guards() >= 3          # checkpoint + scratch (forward), scratch (backward)
+    assert torch.isfinite(y.float()).all() and torch.isfinite(u.grad.float()).all()

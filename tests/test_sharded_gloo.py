@@ -53,7 +53,7 @@ def _init(rank, world, port, timeout_s=60):
                             timeout=datetime.timedelta(seconds=timeout_s))
 
 
-def _worker_parity(rank, world, port, q):
+def _worker_parity(rank, world, port, q, handoff="all_gather"):
     import oracle
     from naju_b200.sharded import naju_scan_time_sharded
     _init(rank, world, port)
@@ -64,7 +64,7 @@ def _worker_parity(rank, world, port, q):
     Dk = torch.tensor(d["Dskip"]).requires_grad_(True)
     h0 = torch.tensor(d["h0"]).requires_grad_(True) if rank == 0 else None
     y, h_end, _ = naju_scan_time_sharded(t["u"], t["fl"], t["il"], t["Bm"], t["Cm"], Dk, None, h0=h0,
-                                         return_final_state=True, local=OracleLocalScan())
+                                         return_final_state=True, local=OracleLocalScan(), handoff=handoff)
     outs = [y]
     grads = [torch.tensor(d["dy"][:, lo:hi])]
     if rank == world - 1:
@@ -80,13 +80,13 @@ def _worker_parity(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_time_sharded_matches_unsharded_oracle(world):
+@pytest.mark.parametrize("world,handoff", [(2, "all_gather"), (3, "all_gather"), (3, "chain")])
+def test_time_sharded_matches_unsharded_oracle(world, handoff):
     import oracle
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker_parity, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker_parity, args=(r, world, port, q, handoff)) for r in range(world)]
     for p in procs:
         p.start()
     res = sorted([q.get(timeout=120) for _ in range(world)], key=lambda r: r["rank"])
