@@ -322,7 +322,7 @@ def run_gpu_arm(args):
     def e2e_step():
         nonlocal host_out
         host_out = scan_fwd_bwd_host(host_in[0], host_in[1], host_in[2], host_in[3], host_in[4], Dk_host,
-                                     host_in[5], rows_per_chunk=1, time_splits=4, out=host_out)
+                                     host_in[5], rows_per_chunk=1, time_splits=2, out=host_out)
         return host_out
 
     e2e_step()
@@ -388,7 +388,7 @@ def _finish(args, world, rank, dev, dist, torch, total_ms, e2e_ms, fwd_ms, bwd_m
                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                            "ms_per_step": e2e_ms, "steps": e2e_steps,
                            "call": "naju_b200.scan_fwd_bwd_host (pinned host tensors in and out, one batch "
-                                   "row per chunk in four time segments, copies overlapped with the kernels)"}
+                                   "row per chunk in two time segments, copies overlapped with the kernels)"}
         if world == 1 and not args.no_cpu_baseline:
             v, ms, cores, sample = cpu_reference_run(3, 1, target_s=2.0)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
