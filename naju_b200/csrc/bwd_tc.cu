@@ -870,9 +870,10 @@ int launch_bwd_tc(const BwdParams& p, const Geometry& g, int act, int gate, int 
         bc == NAJU_BF16))
     return -1000;
   const int64_t ctiles = static_cast<int64_t>(g.B) * g.ndt;
-  // One persistent CTA per SM walks whole channel tiles: with fewer than about a third of the SMs
-  // busy the exact recurrent backward (which spreads over time as well) is the faster one.
-  if (!(ctiles * 3 >= tmah::sm_count() && g.nchunks >= 4)) return -1000;
+  // One persistent CTA per SM walks whole channel tiles: with fewer than about a quarter of the SMs
+  // busy the exact recurrent backward (which spreads over time as well) is the faster one
+  // (measured at D=2048, T=65536: 48 channel tiles 22 against 15 M tokens/s, 32 tiles even).
+  if (!(ctiles * 4 >= tmah::sm_count() && g.nchunks >= 4)) return -1000;
   tcb::Maps maps = {};
   const bool ok =
       (p.u_sd > 1 ? tmah::make_map_tmajor(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_sd, tcb::SLAB, kDT)

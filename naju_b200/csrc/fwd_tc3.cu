@@ -713,9 +713,9 @@ int launch_fwd_tc3(const FwdParams& p, const Geometry& g, int act, int gate, int
   if (!(g.N == tc3::NS && g.TC == tc3::Q && act16 && bc == NAJU_BF16 && (gate == act || gate == NAJU_F32)))
     return -1000;
   if (g.ntiles >= (1LL << 31)) return -1000;
-  // (with fewer than about a third of the SMs busy the ticket-mode kernel, which spreads over time as
+  // (with fewer than about a quarter of the SMs busy the ticket-mode kernel, which spreads over time as
   // well, is the faster one)
-  if (static_cast<int64_t>(g.B) * g.ndt * 3 < tmah::sm_count() || g.nchunks < 4) return -1000;
+  if (static_cast<int64_t>(g.B) * g.ndt * 4 < tmah::sm_count() || g.nchunks < 4) return -1000;
   tc3::Maps maps;
   const bool ok =
       (p.u_sd > 1 ? tmah::make_map_tmajor(&maps.u, p.u, act, g.B, g.T, g.D, p.u_sb, p.u_sd, tc3::SLAB, kDT)
