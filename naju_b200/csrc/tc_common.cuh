@@ -138,25 +138,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t mbar, uint32_t by
 // the phase completes, so the common case costs one instruction and no wake-up delay; only after
 // 64 failed tries does the loop add a nanosleep, which bounds the whole wait to roughly
 // [2^18 x 0.26 us, 2^18 x 4.3 us] = 0.07 .. 1.1 s.
-#define NAJU_STR2(x) #x
-#define NAJU_STR(x) NAJU_STR2(x)
-// One look at the barrier without any suspension (test_wait; try_wait may park the thread for a
-// hardware-chosen time when the phase is still open): true if the phase of parity `parity` has
-// completed.
-__device__ __forceinline__ bool mbar_test_once(uint32_t mbar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(mbar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // One try at the barrier (the hardware may park the thread for a short, bounded time before it
 // answers): true if the phase of parity `parity` has completed.
 __device__ __forceinline__ bool mbar_try_once(uint32_t mbar, uint32_t parity) {
@@ -186,12 +167,8 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t mbar, uint32_t parit
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "@p bra NAJU_MBAR_DONE;\n\t"
       "add.u32 n, n, 1;\n\t"
-#ifdef NAJU_SPIN_SLEEP
-      "nanosleep.u32 " NAJU_STR(NAJU_SPIN_SLEEP) ";\n\t"
-#else
       "setp.gt.u32 q, n, 64;\n\t"
       "@q nanosleep.u32 256;\n\t"
-#endif
       "setp.lt.u32 q, n, %4;\n\t"
       "@q bra NAJU_MBAR_TRY;\n"
       "NAJU_MBAR_DONE:\n\t"
@@ -208,46 +185,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
   return mbar_wait_slow(mbar, parity);
 }
 
-// The same wait for warps with slack (they are waiting most of the time, and a tight polling loop
-// takes issue slots from the working warps of their scheduler): sleep NS nanoseconds between
-// tries.  Bounded like mbar_wait.
-template <int NS>
-__device__ __noinline__ bool mbar_wait_relaxed_slow(uint32_t mbar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, q;\n\t"
-      ".reg .u32 n;\n\t"
-      "mov.u32 n, 0;\n"
-      "NAJU_MBAR_RTRY:\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "@p bra NAJU_MBAR_RDONE;\n\t"
-      "nanosleep.u32 %5;\n\t"
-      "add.u32 n, n, 1;\n\t"
-      "setp.lt.u32 q, n, %4;\n\t"
-      "@q bra NAJU_MBAR_RTRY;\n"
-      "NAJU_MBAR_RDONE:\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(mbar), "r"(parity), "r"(4096u), "r"(1u << 22), "n"(NS)
-      : "memory");
-  return ok != 0;
-}
-template <int NS>
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t mbar, uint32_t parity) {
-  if (mbar_try_once(mbar, parity)) return true;
-  return mbar_wait_relaxed_slow<NS>(mbar, parity);
-}
-
-// For a role that knows its wait is long: look once, sleep FIRST nanoseconds if the phase is not
-// complete yet, then poll every NS nanoseconds (bounded like mbar_wait_relaxed).
-template <int FIRST, int NS>
-__device__ __forceinline__ bool mbar_wait_presleep(uint32_t mbar, uint32_t parity) {
-  if (mbar_try_once(mbar, parity)) return true;
-  if constexpr (FIRST > 0) asm volatile("nanosleep.u32 %0;" ::"n"(FIRST));
-  return mbar_wait_relaxed<NS>(mbar, parity);
-}
+// (Waits that sleep between polls -- 32 ns to 1 us, for the roles with slack -- were measured in both
+// walk kernels and are 1-4 % slower than parking every wait in try_wait.)
 
 // ---- TMA: 3-D tiled load global -> shared, completion counted on an mbarrier.  Plain
 // (single-destination) form only.  The innermost coordinate times the element size must be a
