@@ -366,7 +366,9 @@ def _scan_bwd_op(u: torch.Tensor, f_logit: torch.Tensor, i_logit: torch.Tensor, 
                                                   want_dh0=ph0 is not None)
     if dh0 is None:
         dh0 = du.new_empty(0, dtype=torch.float32)
-    return [du.to(u.dtype), dfl.to(f_logit.dtype), dil.to(i_logit.dtype), dB.to(Bm.dtype), dC.to(Cm.dtype),
+    # (the fake implementation promises contiguous gradients: a du that came back in the layout of a
+    # time-contiguous u is made contiguous here)
+    return [du.to(u.dtype).contiguous(), dfl.to(f_logit.dtype), dil.to(i_logit.dtype), dB.to(Bm.dtype), dC.to(Cm.dtype),
             dD.to(D_skip.dtype), dh0.to(h0.dtype)]
 
 
