@@ -21,14 +21,20 @@ def _round(a, dtype):
     return torch.tensor(a).to(dtype).float().numpy()
 
 
-def test_config1_mixer_shaped_call_under_bf16_autocast():
+@pytest.mark.parametrize("size", [(2, 300, 128, False), (4, 512, 1216, True)])
+def test_config1_mixer_shaped_call_under_bf16_autocast(size):
     """Reproduces how naju/mixer.py:112-122 builds the six scan inputs (random weights, std 0.02,
     bf16 autocast): u is a transposed conv output (time-contiguous memory), B and C are two
     views of one [B,T,2N] tensor, the logits are fp32 next to bf16 activations.  The scan must
-    take them as they come and match the oracle evaluated on exactly those values."""
+    take them as they come and match the oracle evaluated on exactly those values.  The second
+    size is large enough for the walk-along-time tensor-core kernels (76 channel tiles, T a
+    multiple of 8): there u must reach the kernels without a copy and the kernel forms are
+    asserted."""
     from naju_b200 import naju_scan
+    from naju_b200 import scan as S
     torch.manual_seed(1)
-    Bsz, T, d_model, N = 2, 300, 128, 16
+    Bsz, T, d_model, tensor_core = size
+    N = 16
     d_inner = 2 * d_model
     dev = "cuda"
     W_in = torch.randn(2 * d_inner, d_model, device=dev) * 0.02
@@ -57,6 +63,12 @@ def test_config1_mixer_shaped_call_under_bf16_autocast():
     assert y.dtype == torch.bfloat16 and y.shape == (Bsz, T, d_inner)
     dy = torch.randn_like(y)
     y.backward(dy)
+    if tensor_core:
+        torch.cuda.synchronize()
+        assert S.last_kernel_forms() == {"fwd": 3, "bwd": 3}      # NAJU_FORM_TC_WALK
+        pu = S._prepare(leaves[0].detach(), leaves[1].detach(), leaves[2].detach(), Bv.detach(), Cv.detach(), Dz)[0]
+        assert pu.data_ptr() == leaves[0].data_ptr() and pu.stride(1) == 1      # taken as it came
+        assert leaves[0].grad.stride() == leaves[0].stride()                    # and du in the same layout
     a = [t.detach().float().cpu().numpy() for t in (leaves[0], leaves[1], leaves[2], Bv, Cv, Dz)]
     yo = oracle.oracle_fwd(*a)
     g = oracle.oracle_bwd(*a, dy.float().cpu().numpy())
