@@ -466,6 +466,109 @@ def run_decode(args):
         "gpu_launches": L * args.steps}), flush=True)
 
 
+def run_layer(args):
+    """Whole-layer leg (not the headline): the computation of one Naju mixer layer at config 1's
+    size (d_model 1024, expand 2, d_state 16, batch 8, 4096 tokens, bf16 autocast, weights
+    N(0, 0.02^2)), forward + backward, with this library's scan in the place naju/mixer.py:121-122
+    calls `naju_scan`.  The layer is restated here with torch functional ops in the order of
+    naju/mixer.py:112-125 (the reference's module itself is not on this machine); everything but the
+    scan is cuBLAS / cuDNN / torch elementwise, as in the reference.  Reports the layer's time and
+    the scan's share of it."""
+    import torch
+    import torch.nn.functional as F
+    from naju_b200 import naju_scan
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback for the scan)")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    Bsz, T, d_model, N, K = 8, 4096, 1024, 16, 4
+    D = 2 * d_model
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def w(*shape):
+        return (torch.randn(*shape, device=dev, generator=g) * 0.02).requires_grad_(True)
+
+    W_in, W_x, W_f, W_i, W_out = w(2 * D, d_model), w(2 * N, D), w(D, D), w(D, D), w(d_model, D)
+    cw, fw, iw = w(D, 1, K), w(D, 1, K), w(D, 1, K)
+    cb = torch.zeros(D, device=dev, requires_grad=True)
+    f_bias = torch.full((D,), 5.0, device=dev, requires_grad=True)
+    i_bias = torch.full((D,), -2.0, device=dev, requires_grad=True)
+    Dp = torch.full((D,), 0.01, device=dev, requires_grad=True)
+    D_zero = torch.zeros(D, device=dev)
+    params = [W_in, W_x, W_f, W_i, W_out, cw, fw, iw, cb, f_bias, i_bias, Dp]
+    hidden = torch.randn(Bsz, T, d_model, device=dev, generator=g).requires_grad_(True)
+    dout = torch.randn(Bsz, T, d_model, device=dev, generator=g).to(torch.bfloat16)
+    ev = {}
+
+    def layer(timed_scan):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            x, z = F.linear(hidden, W_in).chunk(2, dim=-1)
+            x = F.silu(F.conv1d(x.transpose(1, 2), cw, cb, padding=K - 1, groups=D)[..., :T].transpose(1, 2))
+            Bm, Cm = torch.split(F.linear(x, W_x), [N, N], dim=-1)
+            xt = x.transpose(1, 2)
+            fl = F.linear(x, W_f) + F.conv1d(xt, fw, None, padding=K - 1, groups=D)[..., :T].transpose(1, 2) + f_bias
+            il = F.linear(x, W_i) + F.conv1d(xt, iw, None, padding=K - 1, groups=D)[..., :T].transpose(1, 2) + i_bias
+            if timed_scan:
+                ev["f0"].record()
+            cx = naju_scan(x, fl, il, Bm, Cm, D_zero)
+            if timed_scan:
+                ev["f1"].record()
+            y = (cx * (1.0 / N ** 0.5) + Dp * x) * F.silu(z)
+            out = F.linear(y, W_out)
+        return out
+
+    def step(timed_scan=False):
+        for p in params + [hidden]:
+            p.grad = None
+        out = layer(timed_scan)
+        out.backward(dout)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    steps = max(args.steps, 5)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    layer_ms = e0.elapsed_time(e1) / steps
+    # the scan alone, on the tensors the layer hands it (same layouts and dtypes), forward + backward
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        x, z = F.linear(hidden, W_in).chunk(2, dim=-1)
+        x = F.silu(F.conv1d(x.transpose(1, 2), cw, cb, padding=K - 1, groups=D)[..., :T].transpose(1, 2))
+        Bm, Cm = torch.split(F.linear(x, W_x), [N, N], dim=-1)
+        fl = F.linear(x, W_f) + f_bias
+        il = F.linear(x, W_i) + i_bias
+    leaves = [t.detach().clone(memory_format=torch.preserve_format).requires_grad_(True) for t in (x, fl, il)]
+    bc = torch.cat([Bm, Cm], -1).detach().requires_grad_(True)
+    Bv, Cv = torch.split(bc, [N, N], dim=-1)
+    dy = torch.randn(Bsz, T, D, device=dev, generator=g).to(torch.bfloat16)
+    ts = []
+    for k in range(steps + 3):
+        for p in leaves + [bc]:
+            p.grad = None
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        naju_scan(leaves[0], leaves[1], leaves[2], Bv, Cv, D_zero).backward(dy)
+        b.record()
+        torch.cuda.synchronize()
+        if k >= 3:
+            ts.append(a.elapsed_time(b))
+    scan_ms = sum(ts) / len(ts)
+    print(json.dumps({
+        "metric": "one mixer layer fwd+bwd, d_model 1024, expand 2, N=16, batch 8 x 4096 tokens, bf16 autocast",
+        "value": Bsz * T / (layer_ms / 1e3), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": layer_ms, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "layer: the ops of naju/mixer.py:112-125 restated with torch functional calls, "
+                               "this library's scan in place of naju_scan",
+                   "scan_fwd_bwd_ms": scan_ms, "scan_share": scan_ms / layer_ms,
+                   "u_layout": list(leaves[0].stride()), "logit_dtype": str(leaves[1].dtype)},
+        "gpu_launches": 8 * steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -478,8 +581,9 @@ def main():
     ap.add_argument("--layout", default="reference", choices=["reference", "mixer"],
                     help="reference = contiguous bf16 [B,T,D] tensors (the metric); mixer = u in [B,D,T] memory "
                          "and fp32 logits, as the mixer produces them (a side measurement, not the metric)")
-    ap.add_argument("--workload", default="train", choices=["train", "decode"],
-                    help="train = the headline fwd+bwd scan; decode = the single-token state update")
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "layer"],
+                    help="train = the headline fwd+bwd scan; decode = the single-token state update; "
+                         "layer = one mixer layer at config 1's size with the scan's share of its time")
     args = ap.parse_args()
     args.shape = tuple(int(x) for x in args.shape.split(",")) if args.shape else \
         (CFG["B"], CFG["T"], CFG["D"], CFG["N"])
@@ -488,6 +592,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "layer":
+        run_layer(args)
     else:
         run_gpu_arm(args)
 
