@@ -91,3 +91,37 @@ def test_cpu_tensors_are_rejected():
     with pytest.raises(ValueError):
         resolve_backend("nope")
     assert resolve_backend(None) == "b200" and resolve_backend("chunk") == "b200"
+
+
+def test_descriptor_of_a_time_contiguous_u():
+    """Host logic without a GPU: which layouts of u go to the kernels as they are, what the
+    descriptor says about them, and what the library's stride check accepts."""
+    import torch
+    from naju_b200 import scan as S
+    B, T, D, N = 2, 64, 40, 16
+    u_bdt = torch.zeros(B, D, T, dtype=torch.bfloat16)
+    u = u_bdt.transpose(1, 2)                      # [B,T,D] view of [B,D,T] memory
+    assert S._time_contig(u)
+    assert not S._time_contig(torch.zeros(B, T, D, dtype=torch.bfloat16))                      # ordinary layout
+    assert not S._time_contig(torch.zeros(B, D, 60, dtype=torch.bfloat16).transpose(1, 2))     # T % 8 != 0 (16-bit)
+    assert S._time_contig(torch.zeros(B, D, 60).transpose(1, 2))                               # fp32: T % 4 == 0
+    assert not S._time_contig(torch.zeros(B, D, 1, dtype=torch.bfloat16).transpose(1, 2))      # T = 1: ambiguous
+    z = torch.zeros(B, T, D, dtype=torch.bfloat16)
+    zn = torch.zeros(B, T, N, dtype=torch.bfloat16)
+    d = S._desc(u, z, z, zn, zn)
+    assert (d.u_sb, d.u_st, d.u_sd) == (D * T, 1, T)
+    d0 = S._desc(z, z, z, zn, zn)
+    assert (d0.u_sb, d0.u_st, d0.u_sd) == (T * D, D, 1)
+
+
+def test_stride_check_of_the_time_contiguous_layout(lib):
+    # (every rejection below happens before any CUDA call: all pointers are NULL, so an accepted
+    # descriptor ends at the NULL-pointer check, code -1, and a bad stride at -4)
+    d = _desc()
+    d.u_st, d.u_sd = 1, d.T                   # time-contiguous u: legal
+    assert lib.naju_b200_fwd(d, *([None] * 13)) == -1
+    d.u_sd = d.T - 1                          # channels overlap
+    assert lib.naju_b200_fwd(d, *([None] * 13)) in (-1, -4)
+    d = _desc()
+    d.u_st = 1                                # channel-contiguous u cannot have a time stride of 1
+    assert lib.naju_b200_fwd(d, *([None] * 13)) in (-1, -4)
